@@ -11,7 +11,10 @@
 //
 // Masks: causal; ``window`` > 0 keeps the last ``window`` keys; ``chunk`` > 0 keeps the keys of the query's own
 // chunk, floor(key / chunk) == floor(query / chunk), chunks counted from position 0 of the request.  ``sink``: one
-// float32 per query head: exp(sink) is added to the softmax denominator, nothing to the numerator.
+// float32 per query head: exp(sink) is added to the softmax denominator, nothing to the numerator.  ``softcap`` c > 0:
+// a score s (after the scale) becomes c tanh(s / c).  ``v_is_k``: the values are the keys; a page then holds
+// [Hkv][page_size][hd] only.  ``gate`` (float32 rows [Hq*vd] of stride gate_stride, or null): the output is multiplied
+// element by element by sigmoid(gate); ``out_scale`` multiplies it too; output rows have stride out_stride.
 #include "common.cuh"
 #include <math.h>
 using namespace bspec;
@@ -26,7 +29,9 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
                     const T* __restrict__ cache, const int* __restrict__ qo_indptr,
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int hd, int page_size, float scale,
-                    int window, long long n_pages, int vd, int chunk, const float* __restrict__ sink) {
+                    int window, long long n_pages, int vd, int chunk, const float* __restrict__ sink,
+                    float softcap, int v_is_k, const float* __restrict__ gate, long long gate_stride,
+                    long long out_stride, float out_scale) {
   bspec::pdl_prologue(7);
   __shared__ float qs[WARPS][MAX_HD];
   const int e = blockIdx.y, h = blockIdx.z;
@@ -49,7 +54,7 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
   if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
   const int* table = kv_indices + kv_indptr[e];
   const size_t k_elems = (size_t)Hkv * page_size * hd;          // the keys of a page; its values follow them
-  const size_t page_elems = k_elems + (size_t)Hkv * page_size * vd;
+  const size_t page_elems = k_elems + (v_is_k ? (size_t)0 : (size_t)Hkv * page_size * vd);
   const size_t head_off = (size_t)kvh * page_size * hd;
   constexpr int ND = MAX_HD / 32;
   float acc[ND];
@@ -65,11 +70,13 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
     if (valid) {
       const int page = table[key / page_size];
       koff = (long long)((size_t)page * page_elems + head_off + (size_t)(key % page_size) * hd);
-      voff = (long long)((size_t)page * page_elems + k_elems + ((size_t)kvh * page_size + (size_t)(key % page_size)) * vd);
+      voff = v_is_k ? koff
+                    : (long long)((size_t)page * page_elems + k_elems + ((size_t)kvh * page_size + (size_t)(key % page_size)) * vd);
       const T* kp = cache + koff;
       float dot = 0.f;
       for (int d = 0; d < hd; ++d) dot += qs[warp][d] * to_f32(kp[d]);
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float m_new = fmaxf(m, warp_max(s));        // finite: the chunk holds at least one valid key
     const float p = valid ? expf(s - m_new) : 0.f;
@@ -101,11 +108,16 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
     for (int i = 0; i < ND; ++i) acc[i] *= corr;
   }
   const float inv = 1.f / l;
-  T* op = out + ((size_t)t * Hq + h) * vd;
+  T* op = out + (size_t)t * out_stride + (size_t)h * vd;
+  const float* gp = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)h * vd : nullptr;
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
     const int d = lane + 32 * i;
-    if (d < vd) op[d] = from_f32<T>(acc[i] * inv);
+    if (d < vd) {
+      float o = acc[i] * inv;
+      if (gp != nullptr) o = o / (1.f + expf(-gp[d]));
+      op[d] = from_f32<T>(o * out_scale);
+    }
   }
 }
 }  // namespace
@@ -116,19 +128,23 @@ static int launch_attention_generic(const void* q, long long q_row_stride, void*
                                     const int* qo_indptr, const int* positions, const int* kv_indptr,
                                     const int* kv_indices, int n_entries, int max_q_len, int Hq, int Hkv, int hd,
                                     int page_size, float scale, int window, long long n_pages, int vd, int chunk,
-                                    const float* sink, cudaStream_t stream) {
+                                    const float* sink, float softcap, int v_is_k, const float* gate,
+                                    long long gate_stride, long long out_stride, float out_scale, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return 0;
+  if (v_is_k && vd != hd) return (int)cudaErrorInvalidValue;
   if (hd > MAX_HD || hd <= 0 || vd > MAX_HD || vd <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
   dim3 grid((max_q_len + WARPS - 1) / WARPS, n_entries, Hq);
   if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
   if (dtype == BSPEC_F32)
     BSPEC_LAUNCH((attn_generic_kernel<float>), grid, WARPS * 32, 0, stream, 
         (const float*)q, q_row_stride, (float*)out, (const float*)cache, qo_indptr, positions, kv_indptr, kv_indices,
-        Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink);
+        Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink, softcap, v_is_k, gate, gate_stride, out_stride,
+        out_scale);
   else
     BSPEC_LAUNCH((attn_generic_kernel<__nv_bfloat16>), grid, WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, qo_indptr, positions,
-        kv_indptr, kv_indices, Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink);
+        kv_indptr, kv_indices, Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink, softcap, v_is_k, gate,
+        gate_stride, out_stride, out_scale);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -139,18 +155,21 @@ BSPEC_API int bspec_attention_generic(const void* q, long long q_row_stride, voi
                                       cudaStream_t stream) {
   return launch_attention_generic(q, q_row_stride, out, cache, dtype, qo_indptr, positions, kv_indptr, kv_indices,
                                   n_entries, max_q_len, Hq, Hkv, hd, page_size, scale, window, n_pages, hd, 0, nullptr,
-                                  stream);
+                                  0.f, 0, nullptr, 0, (long long)Hq * hd, 1.f, stream);
 }
 
-// The same with values of their own size ``vd``, a chunk mask (0: none) and a sink per query head (null: none).
+// The same with values of their own size ``vd``, a chunk mask (0: none), a sink per query head (null: none), a soft
+// cap on the scores (0: none), values that are the keys, a sigmoid gate on the output, an output scale and stride.
 BSPEC_API int bspec_attention_masked(const void* q, long long q_row_stride, void* out, const void* cache, int dtype,
                                      const int* qo_indptr, const int* positions, const int* kv_indptr,
                                      const int* kv_indices, int n_entries, int max_q_len, int Hq, int Hkv, int hd,
                                      int vd, int page_size, float scale, int window, int chunk, const float* sink,
-                                     long long n_pages, cudaStream_t stream) {
+                                     long long n_pages, float softcap, int v_is_k, const float* gate,
+                                     long long gate_stride, long long out_stride, float out_scale,
+                                     cudaStream_t stream) {
   return launch_attention_generic(q, q_row_stride, out, cache, dtype, qo_indptr, positions, kv_indptr, kv_indices,
                                   n_entries, max_q_len, Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink,
-                                  stream);
+                                  softcap, v_is_k, gate, gate_stride, out_stride, out_scale, stream);
 }
 
 // ---------------------------------------------------------------- q/k/v preparation
@@ -158,7 +177,8 @@ BSPEC_API int bspec_attention_masked(const void* q, long long q_row_stride, void
 // first ``rot`` numbers of every q and k head (pair (i, i + rot/2), or (2i, 2i+1) with ``interleaved``; cosine and
 // sine times ``magnitude``), divide every q and k head by its root mean square (``norm_eps`` > 0; none otherwise),
 // all in float32; then write q to ``q_out`` [n, Hq*hd] and k and v into the cache page of the token's position.
-// One warp per head.
+// Rows of the input have stride ``ld`` (they may hold more columns).  vd == 0: there are no values (they are the
+// keys); a page then holds keys only.  One warp per head.
 namespace {
 constexpr int PREP_WARPS = 8;
 
@@ -183,7 +203,7 @@ __device__ __forceinline__ void prep_store4(__nv_bfloat16* p, float a, float b, 
 
 template <typename T>
 __global__ void __launch_bounds__(PREP_WARPS * 32)
-qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int vd, const void* __restrict__ bias,
+qkv_prepare_kernel(const float* __restrict__ qkv, long long ld, int Hq, int Hkv, int hd, int vd, const void* __restrict__ bias,
                    int bias_dtype, const float* __restrict__ inv_freq, int rot, int interleaved, float magnitude,
                    float norm_eps, const int* __restrict__ positions, const int* __restrict__ tok_entry,
                    const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, T* __restrict__ q_out,
@@ -195,14 +215,13 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int v
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = blockIdx.y * PREP_WARPS + warp;            // q heads, then k heads, then v heads
   const int pos = positions[t];
-  const int ld = (Hq + Hkv) * hd + Hkv * vd;
-  const bool has = slot < Hq + 2 * Hkv;
+  const bool has = slot < Hq + Hkv + (vd > 0 ? Hkv : 0);
   const bool is_v = slot >= Hq + Hkv;
   const int width = is_v ? vd : hd;
   const int col0 = is_v ? (Hq + Hkv) * hd + (slot - Hq - Hkv) * vd : slot * hd;
   const float* src = qkv + (size_t)t * ld + (has ? col0 : 0);
   float* x = xs[warp];
-  const bool vec = ((hd | vd) & 3) == 0;           // every head starts on a 16-byte boundary: four numbers per lane
+  const bool vec = ((hd | vd | (int)ld) & 3) == 0;           // every head starts on a 16-byte boundary: four numbers per lane
   // the head's numbers are asked for first, so that their way from memory runs under the angles' arithmetic
   float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
   if (has && vec) {
@@ -287,23 +306,23 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int v
 }
 }  // namespace
 
-BSPEC_API int bspec_qkv_prepare(const float* qkv, int n, int Hq, int Hkv, int hd, int vd, const void* bias,
+BSPEC_API int bspec_qkv_prepare(const float* qkv, long long ld, int n, int Hq, int Hkv, int hd, int vd, const void* bias,
                                 int bias_dtype, const float* inv_freq, int rot, int interleaved, float magnitude,
                                 float norm_eps, const int* positions, const int* tok_entry, const int* kv_indptr,
                                 const int* kv_indices, void* q_out, void* cache, int dtype, int page_size, int write_kv,
                                 long long n_pages, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (hd <= 0 || hd > MAX_HD || vd <= 0 || vd > MAX_HD || rot < 0 || rot > hd || rot % 2 != 0 ||
+  if (hd <= 0 || hd > MAX_HD || vd < 0 || vd > MAX_HD || ld < (long long)(Hq + Hkv) * hd + (long long)Hkv * vd || rot < 0 || rot > hd || rot % 2 != 0 ||
       (rot > 0 && inv_freq == nullptr))
     return (int)cudaErrorInvalidValue;
   const dim3 grid(n, (Hq + 2 * Hkv + PREP_WARPS - 1) / PREP_WARPS);
   if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
   if (dtype == BSPEC_F32)
-    BSPEC_LAUNCH((qkv_prepare_kernel<float>), grid, PREP_WARPS * 32, 0, stream, qkv, Hq, Hkv, hd, vd, bias, bias_dtype,
+    BSPEC_LAUNCH((qkv_prepare_kernel<float>), grid, PREP_WARPS * 32, 0, stream, qkv, ld, Hq, Hkv, hd, vd, bias, bias_dtype,
                  inv_freq, rot, interleaved, magnitude, norm_eps, positions, tok_entry, kv_indptr, kv_indices,
                  (float*)q_out, (float*)cache, page_size, write_kv, n_pages);
   else
-    BSPEC_LAUNCH((qkv_prepare_kernel<__nv_bfloat16>), grid, PREP_WARPS * 32, 0, stream, qkv, Hq, Hkv, hd, vd, bias,
+    BSPEC_LAUNCH((qkv_prepare_kernel<__nv_bfloat16>), grid, PREP_WARPS * 32, 0, stream, qkv, ld, Hq, Hkv, hd, vd, bias,
                  bias_dtype, inv_freq, rot, interleaved, magnitude, norm_eps, positions, tok_entry, kv_indptr,
                  kv_indices, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, page_size, write_kv, n_pages);
   return BSPEC_LAUNCH_CHECK();

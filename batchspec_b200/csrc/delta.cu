@@ -313,11 +313,13 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
   }
 }
 
-// out[t, h*V + j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * w[j] * silu(gate[t, h*V + j]); one warp per (token, head).
+// out[t, h*V + j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * w[j] * act(gate[t, h*V + j]), act = silu (gate_kind 0) or
+// sigmoid (1); one warp per (token, head).
 template <typename T>
 __global__ void __launch_bounds__(128)
 gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long gate_stride,
-                     const void* __restrict__ w, int w_dtype, T* __restrict__ out, int n, int H, int V, float eps) {
+                     const void* __restrict__ w, int w_dtype, T* __restrict__ out, int n, int H, int V, float eps,
+                     int gate_kind) {
   bspec::pdl_prologue(62);
   const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (item >= n * H) return;
@@ -329,7 +331,7 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate
   const float r = 1.f / sqrtf(ss / (float)V + eps);
   const float* gp = gate + (size_t)t * gate_stride + (size_t)h * V;
   T* op = out + ((size_t)t * H + h) * V;
-  for (int j = lane; j < V; j += 32) op[j] = from_f32<T>(x[j] * r * load_as_f32(w, w_dtype, j) * silu_f(gp[j]));
+  for (int j = lane; j < V; j += 32) op[j] = from_f32<T>(x[j] * r * load_as_f32(w, w_dtype, j) * (gate_kind == 1 ? 1.f / (1.f + expf(-gp[j])) : silu_f(gp[j])));
 }
 }  // namespace
 
@@ -375,14 +377,15 @@ BSPEC_API int bspec_delta_recurrence(const float* mix, const float* gates, const
 }
 
 BSPEC_API int bspec_gated_rmsnorm(const float* o, const float* gate, long long gate_stride, const void* w, int w_dtype,
-                                  void* out, int out_dtype, int n, int H, int V, float eps, cudaStream_t stream) {
+                                  void* out, int out_dtype, int n, int H, int V, float eps, int gate_kind,
+                                  cudaStream_t stream) {
   if (n <= 0) return 0;
   const int blocks = (n * H + 3) / 4;
   if (out_dtype == BSPEC_F32)
-    BSPEC_LAUNCH((gated_rmsnorm_kernel<float>), blocks, 128, 0, stream, o, gate, gate_stride, w, w_dtype, (float*)out, n, H, V, eps);
+    BSPEC_LAUNCH((gated_rmsnorm_kernel<float>), blocks, 128, 0, stream, o, gate, gate_stride, w, w_dtype, (float*)out, n, H, V, eps, gate_kind);
   else
     BSPEC_LAUNCH((gated_rmsnorm_kernel<__nv_bfloat16>), blocks, 128, 0, stream, o, gate, gate_stride, w, w_dtype,
-                 (__nv_bfloat16*)out, n, H, V, eps);
+                 (__nv_bfloat16*)out, n, H, V, eps, gate_kind);
   return BSPEC_LAUNCH_CHECK();
 }
 

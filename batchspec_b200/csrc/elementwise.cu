@@ -63,7 +63,8 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 template <typename TD, typename TO, typename TW, int VPT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                        const TW* __restrict__ weight, TO* __restrict__ out, int d, float eps,
-                                       float delta_scale, int exact) {
+                                       float delta_scale, int exact, const float* __restrict__ delta_vec,
+                                       int w_scalar) {
   bspec::pdl_prologue(2);
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * d;
@@ -77,8 +78,10 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
       if (delta != nullptr) {
         float dl[4];
         load4<TD>(delta + base + i, dl);
+        float dv[4] = {1.f, 1.f, 1.f, 1.f};
+        if (delta_vec != nullptr) load4<float>(delta_vec + i, dv);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) x[k][j] += delta_scale * dl[j];
+        for (int j = 0; j < 4; ++j) x[k][j] += delta_scale * dv[j] * dl[j];
         store4<float>(resid + base + i, x[k]);
       }
 #pragma unroll
@@ -92,7 +95,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
     const int i = 4 * (threadIdx.x + k * blockDim.x);
     if (i < d) {
       float w[4], y[4];
-      load4<TW>(weight + i, w);
+      if (w_scalar) w[0] = w[1] = w[2] = w[3] = to_f32(weight[0]);
+      else load4<TW>(weight + i, w);
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         y[j] = exact ? x[k][j] * r * w[j] : to_f32(from_f32<TO>(to_f32(from_f32<TO>(x[k][j] * r)) * w[j]));
@@ -104,7 +108,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const void* __restrict__ weight, int w_dtype, TO* __restrict__ out, int d,
-                                   float eps, float delta_scale, int exact) {
+                                   float eps, float delta_scale, int exact, const float* __restrict__ delta_vec,
+                                   int w_scalar) {
   bspec::pdl_prologue(2);
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * d;
@@ -112,7 +117,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = resid[base + i];
     if (delta != nullptr) {
-      v += delta_scale * to_f32(delta[base + i]);
+      v += delta_scale * (delta_vec != nullptr ? delta_vec[i] : 1.f) * to_f32(delta[base + i]);
       resid[base + i] = v;
     }
     ss += v * v;
@@ -121,14 +126,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
   const float r = exact ? 1.f / sqrtf(total / (float)d + eps) : rsqrtf(total / (float)d + eps);
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     const float n = resid[base + i] * r;
-    const float w = load_as_f32(weight, w_dtype, i);
+    const float w = load_as_f32(weight, w_dtype, w_scalar ? 0 : i);
     out[base + i] = exact ? from_f32<TO>(n * w) : from_f32<TO>(to_f32(from_f32<TO>(n)) * w);
   }
 }
 
 template <typename TD, typename TO, typename TW>
 static void launch_add_rmsnorm_vec(float* resid, const void* delta, const void* weight, void* out, int n, int d,
-                                   float eps, float delta_scale, int exact, cudaStream_t stream) {
+                                   float eps, float delta_scale, int exact, const float* delta_vec, int w_scalar,
+                                   cudaStream_t stream) {
   const int quads = d / 4;
   int threads = quads >= 1024 ? 1024 : ((quads + 31) / 32) * 32;
   // Many rows (a prompt): four quads per thread, so that a thread has more loads in flight and several rows share
@@ -137,30 +143,31 @@ static void launch_add_rmsnorm_vec(float* resid, const void* delta, const void* 
   if (sizeof(TO) == 2 && n >= 512 && quads >= 128) threads = (((quads + 3) / 4 + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   const int vpt = (quads + threads - 1) / threads;
-#define LV(V) BSPEC_LAUNCH((add_rmsnorm_vec_kernel<TD, TO, TW, V>), n, threads, 0, stream, resid, (const TD*)delta, (const TW*)weight, (TO*)out, d, eps, delta_scale, exact)
+#define LV(V) BSPEC_LAUNCH((add_rmsnorm_vec_kernel<TD, TO, TW, V>), n, threads, 0, stream, resid, (const TD*)delta, (const TW*)weight, (TO*)out, d, eps, delta_scale, exact, delta_vec, w_scalar)
   if (vpt <= 1) LV(1); else if (vpt <= 2) LV(2); else LV(4);
 #undef LV
 }
 
-// delta_scale multiplies delta in the sum.  exact != 0: one rounding, resid / sqrt(mean + eps) * w in float32 and
+// delta_scale multiplies delta in the sum, and so does delta_vec[column] (float32 [d]) when given.  w_scalar != 0: the
+// weight is one number for all columns.  exact != 0: one rounding, resid / sqrt(mean + eps) * w in float32 and
 // then the cast; 0: the cast to the output type comes before the product with w, which is taken in that type.
 BSPEC_API int bspec_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const void* weight, int w_dtype,
                                 void* out, int out_dtype, int n, int d, float eps, float delta_scale, int exact,
-                                cudaStream_t stream) {
+                                const float* delta_vec, int w_scalar, cudaStream_t stream) {
   if (n <= 0) return 0;
   const bool same = delta_dtype == out_dtype;
   if (same && d % 4 == 0 && d <= 4 * 4 * 1024) {
     if (out_dtype == BSPEC_F32) {
-      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<float, float, float>(resid, delta, weight, out, n, d, eps, delta_scale, exact, stream);
-      else launch_add_rmsnorm_vec<float, float, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, delta_scale, exact, stream);
+      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<float, float, float>(resid, delta, weight, out, n, d, eps, delta_scale, exact, delta_vec, w_scalar, stream);
+      else launch_add_rmsnorm_vec<float, float, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, delta_scale, exact, delta_vec, w_scalar, stream);
     } else {
-      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, float>(resid, delta, weight, out, n, d, eps, delta_scale, exact, stream);
-      else launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, delta_scale, exact, stream);
+      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, float>(resid, delta, weight, out, n, d, eps, delta_scale, exact, delta_vec, w_scalar, stream);
+      else launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, delta_scale, exact, delta_vec, w_scalar, stream);
     }
     return BSPEC_LAUNCH_CHECK();
   }
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-#define L(TD, TO) BSPEC_LAUNCH((add_rmsnorm_kernel<TD, TO>), n, threads, 0, stream, resid, (const TD*)delta, weight, w_dtype, (TO*)out, d, eps, delta_scale, exact)
+#define L(TD, TO) BSPEC_LAUNCH((add_rmsnorm_kernel<TD, TO>), n, threads, 0, stream, resid, (const TD*)delta, weight, w_dtype, (TO*)out, d, eps, delta_scale, exact, delta_vec, w_scalar)
   if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_F32) L(float, float);
   else if (delta_dtype == BSPEC_BF16 && out_dtype == BSPEC_BF16) L(__nv_bfloat16, __nv_bfloat16);
   else if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_BF16) L(float, __nv_bfloat16);
@@ -283,50 +290,54 @@ BSPEC_API int bspec_add_layernorm(float* resid, const void* delta, int delta_dty
 template <typename TD>
 __global__ void gather_rows_add_kernel(const float* __restrict__ resid, const TD* __restrict__ pending,
                                        const int* __restrict__ rows, float* __restrict__ out, int d, int n_src,
-                                       float scale) {
+                                       float scale, const float* __restrict__ vec) {
   bspec::pdl_prologue(3);
   if (!bspec::in_range(rows[blockIdx.x], n_src, 102)) return;
   const size_t src = (size_t)rows[blockIdx.x] * d, dst = (size_t)blockIdx.x * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = resid[src + i];
-    if (pending != nullptr) v += scale * to_f32(pending[src + i]);
+    if (pending != nullptr) v += scale * (vec != nullptr ? vec[i] : 1.f) * to_f32(pending[src + i]);
     out[dst + i] = v;
   }
 }
 
 BSPEC_API int bspec_gather_rows_add(const float* resid, const void* pending, int pending_dtype, const int* rows,
-                                    float* out, int n_out, int d, int n_src, float scale, cudaStream_t stream) {
+                                    float* out, int n_out, int d, int n_src, float scale, const float* vec,
+                                    cudaStream_t stream) {
   if (n_out <= 0) return 0;
   if (pending_dtype == BSPEC_F32)
-    BSPEC_LAUNCH((gather_rows_add_kernel<float>), n_out, 256, 0, stream, resid, (const float*)pending, rows, out, d, n_src, scale);
+    BSPEC_LAUNCH((gather_rows_add_kernel<float>), n_out, 256, 0, stream, resid, (const float*)pending, rows, out, d, n_src, scale, vec);
   else
-    BSPEC_LAUNCH((gather_rows_add_kernel<__nv_bfloat16>), n_out, 256, 0, stream, resid, (const __nv_bfloat16*)pending, rows, out, d, n_src, scale);
+    BSPEC_LAUNCH((gather_rows_add_kernel<__nv_bfloat16>), n_out, 256, 0, stream, resid, (const __nv_bfloat16*)pending, rows, out, d, n_src, scale, vec);
   return BSPEC_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------- residual update
-// resid += scale * pending (if pending) + extra (if extra), float32, in this order.
+// resid += scale * vec[column] * pending (if pending; vec float32 [d] or null) + extra (if extra), float32, in this order.
 template <typename TD>
 __global__ void residual_update_kernel(float* __restrict__ resid, const TD* __restrict__ pending, float scale,
-                                       const float* __restrict__ extra, size_t total) {
+                                       const float* __restrict__ extra, size_t total,
+                                       const float* __restrict__ vec, int d) {
   bspec::pdl_prologue(18);
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     float v = resid[i];
-    if (pending != nullptr) v += scale * to_f32(pending[i]);
+    if (pending != nullptr) v += scale * (vec != nullptr ? vec[i % d] : 1.f) * to_f32(pending[i]);
     if (extra != nullptr) v += extra[i];
     resid[i] = v;
   }
 }
 
 BSPEC_API int bspec_residual_update(float* resid, const void* pending, int pending_dtype, float scale,
-                                    const float* extra, long long total, cudaStream_t stream) {
+                                    const float* extra, long long total, const float* vec, int d,
+                                    cudaStream_t stream) {
   if (total <= 0) return 0;
+  if (vec != nullptr && d <= 0) return (int)cudaErrorInvalidValue;
   const size_t want = ((size_t)total + 255) / 256, cap = (size_t)bspec::sm_count() * 16;
   const int blocks = (int)(want > cap ? cap : want);
   if (pending_dtype == BSPEC_F32)
-    BSPEC_LAUNCH((residual_update_kernel<float>), blocks, 256, 0, stream, resid, (const float*)pending, scale, extra, (size_t)total);
+    BSPEC_LAUNCH((residual_update_kernel<float>), blocks, 256, 0, stream, resid, (const float*)pending, scale, extra, (size_t)total, vec, d);
   else
-    BSPEC_LAUNCH((residual_update_kernel<__nv_bfloat16>), blocks, 256, 0, stream, resid, (const __nv_bfloat16*)pending, scale, extra, (size_t)total);
+    BSPEC_LAUNCH((residual_update_kernel<__nv_bfloat16>), blocks, 256, 0, stream, resid, (const __nv_bfloat16*)pending, scale, extra, (size_t)total, vec, d);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -339,7 +350,15 @@ __device__ __forceinline__ size_t gate_col(size_t col, int inter, int group) {
 __device__ __forceinline__ size_t up_col(size_t col, int inter, int group) {
   return group > 0 ? (col / group) * 2 * group + group + (col % group) : inter + col;
 }
-// act 0: silu(gate) * up;  act 1: relu(gate) * up
+// act 0: silu(gate) * up;  act 1: relu(gate) * up;  act 2: gelu(gate) * up in the tanh form,
+// gelu(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+// the same through the fast exponential: tanh(u) = 1 - 2 / (1 + exp(2u)), so 0.5 (1 + tanh u) = 1 / (1 + exp(-2u))
+__device__ __forceinline__ float gelu_tanh_fast(float z) {
+  return __fdividef(z, 1.f + __expf(-1.5957691216057308f * (z + 0.044715f * z * z * z)));
+}
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int inter, size_t total, int group, int act) {
   bspec::pdl_prologue(4);
@@ -348,7 +367,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int 
     const size_t row = idx / inter, col = idx - row * inter;
     const float g = to_f32(u[row * 2 * inter + gate_col(col, inter, group)]);
     const float up = to_f32(u[row * 2 * inter + up_col(col, inter, group)]);
-    const float s = act == 1 ? fmaxf(g, 0.f) : g / (1.f + expf(-g));
+    const float s = act == 1 ? fmaxf(g, 0.f) : (act == 2 ? gelu_tanh_f(g) : g / (1.f + expf(-g)));
     m[idx] = from_f32<T>(s * up);
   }
 }
@@ -375,8 +394,8 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ u, __nv
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float ga = __low2float(g2[j]), gb = __high2float(g2[j]);
-      const float sa = act == 1 ? fmaxf(ga, 0.f) : __fdividef(ga, 1.f + __expf(-ga));
-      const float sb = act == 1 ? fmaxf(gb, 0.f) : __fdividef(gb, 1.f + __expf(-gb));
+      const float sa = act == 1 ? fmaxf(ga, 0.f) : (act == 2 ? gelu_tanh_fast(ga) : __fdividef(ga, 1.f + __expf(-ga)));
+      const float sb = act == 1 ? fmaxf(gb, 0.f) : (act == 2 ? gelu_tanh_fast(gb) : __fdividef(gb, 1.f + __expf(-gb)));
       o2[j] = __floats2bfloat162_rn(sa * __low2float(u2[j]), sb * __high2float(u2[j]));
     }
     *reinterpret_cast<uint4*>(m + (size_t)row * inter + col) = ov;
@@ -414,6 +433,84 @@ BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter
 // relu(gate) * up, the layouts of silu_mul
 BSPEC_API int bspec_relu_mul(const void* u, void* m, int dtype, int n, int inter, int group, cudaStream_t stream) {
   return launch_gated_mul(u, m, dtype, n, inter, group, 1, stream);
+}
+
+// gelu(gate) * up with the tanh form of gelu, the layouts of silu_mul
+BSPEC_API int bspec_gelu_tanh_mul(const void* u, void* m, int dtype, int n, int inter, int group, cudaStream_t stream) {
+  return launch_gated_mul(u, m, dtype, n, inter, group, 2, stream);
+}
+
+// ---------------------------------------------------------------- hashed bigram rows
+// resid[t, :] += table[row(t), :] with row = (previous token * mul_prev + token * mul_cur) mod buckets, and row =
+// buckets (the table's last row) for the token at position 0.  The previous token of a portion's first token is
+// prev[slot of its request] (an int32 per request), which the same block then sets to the portion's last token, so
+// that no block reads a number another block writes.  One block per token.
+template <typename T>
+__global__ void bigram_add_kernel(float* __restrict__ resid, const int* __restrict__ ids, const int* __restrict__ positions,
+                                  const int* __restrict__ tok_entry, const int* __restrict__ qo_indptr,
+                                  const int* __restrict__ state_slots, int* __restrict__ prev, long long prev_stride,
+                                  const T* __restrict__ table, int d, int vocab, int buckets, int mul_prev,
+                                  int mul_cur) {
+  bspec::pdl_prologue(63);
+  __shared__ int s_row;
+  const int t = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const int e = tok_entry[t], first = qo_indptr[e];
+    int before;
+    if (t > first) {
+      before = ids[t - 1];
+    } else {
+      int* p = prev + (size_t)state_slots[e] * prev_stride;
+      before = *p;
+      *p = ids[qo_indptr[e + 1] - 1];
+    }
+    const int id = ids[t];
+    long long row = buckets;
+    if (positions[t] > 0) {
+      row = ((long long)before * mul_prev + (long long)id * mul_cur) % buckets;
+      if (row < 0) row += buckets;
+    }
+    const bool ok = id >= 0 && id < vocab && before >= 0 && before < vocab;
+    (void)bspec::in_range(id, vocab, 101);
+    s_row = ok ? (int)row : -1;
+  }
+  __syncthreads();
+  const int row = s_row;
+  if (row < 0) return;
+  const T* src = table + (size_t)row * d;
+  float* o = resid + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] += to_f32(src[i]);
+}
+
+BSPEC_API int bspec_bigram_add(float* resid, const int* ids, const int* positions, const int* tok_entry,
+                               const int* qo_indptr, const int* state_slots, int* prev, long long prev_stride,
+                               const void* table, int table_dtype, int n, int d, int vocab, int buckets, int mul_prev,
+                               int mul_cur, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (buckets <= 0) return (int)cudaErrorInvalidValue;
+  const int threads = d >= 1024 ? 256 : 128;
+  if (table_dtype == BSPEC_F32)
+    BSPEC_LAUNCH((bigram_add_kernel<float>), n, threads, 0, stream, resid, ids, positions, tok_entry, qo_indptr,
+                 state_slots, prev, prev_stride, (const float*)table, d, vocab, buckets, mul_prev, mul_cur);
+  else
+    BSPEC_LAUNCH((bigram_add_kernel<__nv_bfloat16>), n, threads, 0, stream, resid, ids, positions, tok_entry,
+                 qo_indptr, state_slots, prev, prev_stride, (const __nv_bfloat16*)table, d, vocab, buckets, mul_prev,
+                 mul_cur);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// In place on float32: x *= factor.
+__global__ void scale_kernel(float* __restrict__ x, size_t total, float factor) {
+  bspec::pdl_prologue(64);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    x[i] *= factor;
+}
+
+BSPEC_API int bspec_scale(float* x, long long total, float factor, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const size_t want = ((size_t)total + 255) / 256, cap = (size_t)bspec::sm_count() * 16;
+  BSPEC_LAUNCH(scale_kernel, (int)(want > cap ? cap : want), 256, 0, stream, x, (size_t)total, factor);
+  return BSPEC_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------- clamped GLU:  g sigmoid(alpha g) (u + 1)

@@ -82,6 +82,7 @@ __device__ __forceinline__ float glu_combine(int kind, float alpha, float limit,
     return g / (1.f + expf(-alpha * g)) * (u + 1.f);
   }
   if (kind == 3) return fmaxf(g, 0.f) * u;
+  if (kind == 4) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;   // gelu, tanh form
   return g / (1.f + expf(-g)) * u;
 }
 
@@ -445,7 +446,7 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
   if (glu && (N % 16 != 0)) return (int)cudaErrorInvalidValue;
   GemmParams p;
   p.C = C; p.status = status;
-  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu == 2 ? 2 : (glu == 3 ? 3 : (glu ? 1 : 0));
+  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu == 2 ? 2 : (glu == 3 ? 3 : (glu == 4 ? 4 : (glu ? 1 : 0)));
   p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
   p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
   p.rope_freq = nullptr; p.positions = p.tok_entry = p.kv_indptr = p.kv_indices = nullptr; p.cache = nullptr;
@@ -510,7 +511,7 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
 
 // C = X W^T.  `status`: one int on the device, 0 unless a bounded wait ran out.
 // glu != 0: the rows of W come in groups of 16 (8 gate rows, then the 8 matching up rows; N a multiple of 16) and
-// C is [M, N/2] = silu(gate) * up (glu 1) or relu(gate) * up (glu 3).
+// C is [M, N/2] = silu(gate) * up (glu 1), relu(gate) * up (glu 3) or gelu(gate) * up in the tanh form (glu 4).
 BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu,
                             int* status, int sm_count, cudaStream_t stream) {
   return launch_gemm(X, W, C, M, N, K, out_f32, glu, status, sm_count, nullptr, stream);

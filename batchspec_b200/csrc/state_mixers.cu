@@ -1,0 +1,267 @@
+// Two recurrent mixers whose state per request has a fixed size, float32 throughout.
+//
+//   lightning_recurrence   linear attention with a fixed decay per head:
+//                              S <- decay_h S + k v^T,  o = S^T q        S: [dim x vdim] per head
+//                          q, k, v are the silu of float32 projection columns.
+//   scan_conv              short causal convolution per channel with bias, then silu (inputs before the portion come
+//                          from the request's state)
+//   selective_scan         per channel c and state n:  S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n,
+//                              y_c = sum_n S[c, n] C_n + D_c x_c,  out_c = y_c silu(z_c),  dt = softplus(raw + bias),
+//                              A = -exp(A_log)
+//
+// A step holds portions of several requests (qo_indptr, state_slots); a portion of one token is a decode step.  Every
+// sum runs in an order fixed by the sizes alone, so a position's result does not depend on how the request was cut
+// or on what else is in the step.
+#include "common.cuh"
+#include <math.h>
+using namespace bspec;
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------- lightning attention
+// Block: COLS value columns of one head of one request, 8 lanes per column; lane r of a column keeps rows
+// r, r + 8, ... of that column of S in registers (NR of them).  Tokens are staged TT at a time in shared memory.
+// State of a request: [H][vdim][dim] float32 at state + slot * state_stride.
+constexpr int LT_COLS = 16;
+constexpr int LT_TT = 16;
+constexpr int LT_MAX_DIM = 256;
+
+template <int NR>
+__global__ void __launch_bounds__(LT_COLS * 8)
+lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_off, int k_off, int v_off,
+                            const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
+                            const int* __restrict__ qo_indptr, const int* __restrict__ state_slots,
+                            float* __restrict__ out, int H, int dim, int vdim) {
+  bspec::pdl_prologue_late(65);
+  __shared__ float qs[LT_TT][LT_MAX_DIM];
+  __shared__ float ks[LT_TT][LT_MAX_DIM];
+  __shared__ float vs[LT_TT][LT_COLS];
+  const int e = blockIdx.z, h = blockIdx.y;
+  const int col = threadIdx.x >> 3, r = threadIdx.x & 7;
+  const int j = blockIdx.x * LT_COLS + col;                 // value column of the head
+  const bool live = j < vdim;
+  const int t0 = qo_indptr[e], nt = qo_indptr[e + 1] - t0;
+  const float d = decay[h];
+  float* sp = state + (size_t)state_slots[e] * state_stride + ((size_t)h * vdim + (live ? j : 0)) * dim;
+  float s[NR];
+#pragma unroll
+  for (int m = 0; m < NR; ++m) {
+    const int i = r + 8 * m;
+    s[m] = (live && i < dim) ? sp[i] : 0.f;
+  }
+  for (int base = 0; base < nt; base += LT_TT) {
+    const int cnt = min(LT_TT, nt - base);
+    __syncthreads();
+    for (int x = threadIdx.x; x < cnt * dim; x += blockDim.x) {
+      const int tt = x / dim, i = x - tt * dim;
+      const float* row = proj + (size_t)(t0 + base + tt) * ld + (size_t)h * dim + i;
+      qs[tt][i] = silu_f(row[q_off]);
+      ks[tt][i] = silu_f(row[k_off]);
+    }
+    for (int x = threadIdx.x; x < cnt * LT_COLS; x += blockDim.x) {
+      const int tt = x / LT_COLS, c = x - tt * LT_COLS;
+      const int jj = blockIdx.x * LT_COLS + c;
+      vs[tt][c] = jj < vdim ? silu_f(proj[(size_t)(t0 + base + tt) * ld + v_off + (size_t)h * vdim + jj]) : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < cnt; ++tt) {
+      const float vj = vs[tt][col];
+      float acc = 0.f;
+#pragma unroll
+      for (int m = 0; m < NR; ++m) {
+        const int i = r + 8 * m;
+        if (i < dim) {
+          s[m] = d * s[m] + ks[tt][i] * vj;
+          acc += s[m] * qs[tt][i];
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (live && r == 0) out[(size_t)(t0 + base + tt) * H * vdim + (size_t)h * vdim + j] = acc;
+    }
+  }
+  bspec::pdl_launch_dependents();
+  if (live) {
+#pragma unroll
+    for (int m = 0; m < NR; ++m) {
+      const int i = r + 8 * m;
+      if (i < dim) sp[i] = s[m];
+    }
+  }
+}
+
+// ---------------------------------------------------------------- selective scan
+// xz [n, ld]: columns [x: inner | z: inner] of the in-projection.  State of a request at state + slot * stride:
+// [N][inner] float32 (the scan's S, state index major), then at tail_off [(taps-1)][inner] the last inputs of the
+// convolution, oldest first.
+
+// xc[t, c] = silu(bias[c] + sum_j conv[c, j] * x[t - (taps-1) + j, c]); one thread per (token, channel).
+template <typename T>
+__global__ void __launch_bounds__(256)
+scan_conv_kernel(const float* __restrict__ xz, long long ld, const void* __restrict__ conv, const void* __restrict__ bias,
+                 int w_dtype, const float* __restrict__ state, long long state_stride, long long tail_off,
+                 const int* __restrict__ qo_indptr, const int* __restrict__ tok_entry,
+                 const int* __restrict__ state_slots, float* __restrict__ xc, T* __restrict__ xc_run, int inner,
+                 int taps) {
+  bspec::pdl_prologue(66);
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= inner) return;
+  const int e = tok_entry[t];
+  const int i = t - qo_indptr[e];
+  const float* tail = state + (size_t)state_slots[e] * state_stride + tail_off;
+  float y = load_as_f32(bias, w_dtype, c);
+  for (int j = 0; j < taps; ++j) {                           // oldest input first
+    const int rel = i - (taps - 1 - j);
+    const float x = rel >= 0 ? xz[(size_t)(t - (taps - 1 - j)) * ld + c] : tail[(size_t)(rel + taps - 1) * inner + c];
+    y += load_as_f32(conv, w_dtype, (size_t)c * taps + j) * x;
+  }
+  const float v = silu_f(y);
+  xc[(size_t)t * inner + c] = v;
+  if (xc_run != nullptr) xc_run[(size_t)t * inner + c] = from_f32<T>(v);
+}
+
+constexpr int SC_THREADS = 128;
+constexpr int SC_TT = 8;
+constexpr int SC_MAX_N = 256;
+
+// LN lanes per channel; lane l keeps states l, l + LN, ... (NPL of them) of its channel in registers.
+template <typename T, int NPL, int LN>
+__global__ void __launch_bounds__(SC_THREADS)
+selective_scan_kernel(const float* __restrict__ xz, long long ld, const float* __restrict__ xc,
+                      const float* __restrict__ dt_raw, const float* __restrict__ bc, long long ld_bc,
+                      const void* __restrict__ a_log, const void* __restrict__ dvec, const void* __restrict__ dt_bias,
+                      int w_dtype, float* __restrict__ state, long long state_stride, long long tail_off,
+                      const int* __restrict__ qo_indptr, const int* __restrict__ state_slots, T* __restrict__ out,
+                      long long out_stride, float out_scale, int inner, int N, int taps) {
+  bspec::pdl_prologue_late(67);
+  __shared__ float bcs[SC_TT][2 * SC_MAX_N];
+  const int e = blockIdx.y;
+  const int lane = threadIdx.x % LN;
+  const int c = blockIdx.x * (SC_THREADS / LN) + threadIdx.x / LN;
+  const bool live = c < inner;
+  const int cc = live ? c : 0;
+  const int t0 = qo_indptr[e], nt = qo_indptr[e + 1] - t0;
+  float* sp = state + (size_t)state_slots[e] * state_stride;
+  float s[NPL], a2[NPL];
+#pragma unroll
+  for (int m = 0; m < NPL; ++m) {
+    const int n = lane + LN * m;
+    const bool has = live && n < N;
+    s[m] = has ? sp[(size_t)n * inner + cc] : 0.f;
+    // exp(dt A) = 2^(dt A log2 e)
+    a2[m] = has ? -expf(load_as_f32(a_log, w_dtype, (size_t)cc * N + n)) * 1.4426950408889634f : 0.f;
+  }
+  const float dskip = load_as_f32(dvec, w_dtype, cc), dtb = load_as_f32(dt_bias, w_dtype, cc);
+  for (int base = 0; base < nt; base += SC_TT) {
+    const int cnt = min(SC_TT, nt - base);
+    __syncthreads();
+    for (int x = threadIdx.x; x < cnt * 2 * N; x += blockDim.x) {
+      const int tt = x / (2 * N), k = x - tt * 2 * N;
+      bcs[tt][k] = bc[(size_t)(t0 + base + tt) * ld_bc + k];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < cnt; ++tt) {
+      const size_t t = (size_t)(t0 + base + tt);
+      const float x = xc[t * inner + cc];
+      const float dt = softplus_f(dt_raw[t * inner + cc] + dtb);
+      const float dx = dt * x;
+      float y = 0.f;
+#pragma unroll
+      for (int m = 0; m < NPL; ++m) {
+        const int n = lane + LN * m;
+        if (n < N) {
+          s[m] = exp2f(dt * a2[m]) * s[m] + dx * bcs[tt][n];
+          y += s[m] * bcs[tt][N + n];
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < LN; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (live && lane == 0) {
+        const float z = xz[t * ld + inner + cc];
+        out[t * out_stride + cc] = from_f32<T>((y + dskip * x) * silu_f(z) * out_scale);
+      }
+    }
+  }
+  bspec::pdl_launch_dependents();
+  if (!live) return;
+#pragma unroll
+  for (int m = 0; m < NPL; ++m) {
+    const int n = lane + LN * m;
+    if (n < N) sp[(size_t)n * inner + cc] = s[m];
+  }
+  if (lane == 0) {
+    // the convolution's last taps-1 inputs, oldest first: rows of this portion, and before them what the state held
+    float* tail = sp + tail_off;
+    for (int u = 0; u < taps - 1; ++u) {
+      const int rel = nt - (taps - 1) + u;
+      tail[(size_t)u * inner + cc] = rel >= 0 ? xz[(size_t)(t0 + rel) * ld + cc] : tail[(size_t)(u + nt) * inner + cc];
+    }
+  }
+}
+}  // namespace
+
+BSPEC_API int bspec_lightning_recurrence(const float* proj, long long ld, int q_off, int k_off, int v_off,
+                                         const float* decay, float* state, long long state_stride,
+                                         const int* qo_indptr, const int* state_slots, float* out, int n_entries, int H,
+                                         int dim, int vdim, cudaStream_t stream) {
+  if (n_entries <= 0) return 0;
+  if (dim <= 0 || dim > LT_MAX_DIM || vdim <= 0 || H <= 0 || H > 65535 || n_entries > 65535)
+    return (int)cudaErrorInvalidValue;
+  const dim3 grid((vdim + LT_COLS - 1) / LT_COLS, H, n_entries);
+#define LL(NR)                                                                                                     \
+  BSPEC_LAUNCH_SERIALIZED((lightning_recurrence_kernel<NR>), grid, LT_COLS * 8, 0, stream, proj, ld, q_off, k_off, \
+                          v_off, decay, state, state_stride, qo_indptr, state_slots, out, H, dim, vdim)
+  if (dim <= 32) LL(4); else if (dim <= 64) LL(8); else if (dim <= 128) LL(16); else LL(32);
+#undef LL
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_scan_conv(const float* xz, long long ld, const void* conv, const void* bias, int w_dtype,
+                              const float* state, long long state_stride, long long tail_off, const int* qo_indptr,
+                              const int* tok_entry, const int* state_slots, float* xc, void* xc_run, int run_dtype,
+                              int n, int inner, int taps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (inner <= 0 || taps < 1) return (int)cudaErrorInvalidValue;
+  const int threads = inner >= 256 ? 256 : ((inner + 31) / 32) * 32;
+  const dim3 grid(n, (inner + threads - 1) / threads);
+  if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
+  if (run_dtype == BSPEC_F32)
+    BSPEC_LAUNCH((scan_conv_kernel<float>), grid, threads, 0, stream, xz, ld, conv, bias, w_dtype, state, state_stride,
+                 tail_off, qo_indptr, tok_entry, state_slots, xc, (float*)nullptr, inner, taps);
+  else
+    BSPEC_LAUNCH((scan_conv_kernel<__nv_bfloat16>), grid, threads, 0, stream, xz, ld, conv, bias, w_dtype, state,
+                 state_stride, tail_off, qo_indptr, tok_entry, state_slots, xc, (__nv_bfloat16*)xc_run, inner, taps);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_selective_scan(const float* xz, long long ld, const float* xc, const float* dt_raw, const float* bc,
+                                   long long ld_bc, const void* a_log, const void* dvec, const void* dt_bias,
+                                   int w_dtype, float* state, long long state_stride, long long tail_off,
+                                   const int* qo_indptr, const int* state_slots, void* out, int out_dtype,
+                                   long long out_stride, float out_scale, int n_entries, int inner, int N, int taps,
+                                   cudaStream_t stream) {
+  if (n_entries <= 0) return 0;
+  if (inner <= 0 || N <= 0 || N > SC_MAX_N || taps < 1 || n_entries > 65535) return (int)cudaErrorInvalidValue;
+#define LS(T, NPL, LN)                                                                                               \
+  BSPEC_LAUNCH_SERIALIZED((selective_scan_kernel<T, NPL, LN>),                                                       \
+                          dim3((inner + SC_THREADS / LN - 1) / (SC_THREADS / LN), n_entries), SC_THREADS, 0, stream, \
+                          xz, ld, xc, dt_raw, bc, ld_bc, a_log, dvec, dt_bias, w_dtype, state, state_stride, tail_off, \
+                          qo_indptr, state_slots, (T*)out, out_stride, out_scale, inner, N, taps)
+#define LSN(T)                                                                                                       \
+  do {                                                                                                               \
+    if (N <= 16) LS(T, 16, 1); else if (N <= 32) LS(T, 32, 1); else if (N <= 64) LS(T, 32, 2);                       \
+    else if (N <= 128) LS(T, 32, 4); else LS(T, 32, 8);                                                              \
+  } while (0)
+  if (out_dtype == BSPEC_F32) LSN(float); else LSN(__nv_bfloat16);
+#undef LSN
+#undef LS
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_state_mixers)
+BSPEC_DEFINE_BOUNDS_REPORT(bspec_bounds_report_state_mixers)

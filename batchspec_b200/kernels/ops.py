@@ -41,24 +41,36 @@ def _dtype_code(t: torch.dtype) -> int:
 _SIGNATURES = {
     "bspec_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "bspec_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
-                          c_int, c_void_p],
-    "bspec_gather_rows_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
-    "bspec_residual_update": [c_void_p, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p],
+                          c_int, c_void_p, c_int, c_void_p],
+    "bspec_gather_rows_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
+                              c_void_p],
+    "bspec_residual_update": [c_void_p, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p, c_int, c_void_p],
+    "bspec_gelu_tanh_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_bigram_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_scale": [c_void_p, c_longlong, c_float, c_void_p],
+    "bspec_lightning_recurrence": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_scan_conv": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_selective_scan": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                             c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                             c_longlong, c_float, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_relu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "bspec_qkv_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float,
+    "bspec_qkv_prepare": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float,
                           c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_longlong, c_void_p],
     "bspec_attention_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
-                               c_longlong, c_void_p],
+                               c_longlong, c_float, c_int, c_void_p, c_longlong, c_longlong, c_float, c_void_p],
     "bspec_delta_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                             c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                             c_int, c_int, c_int, c_float, c_float, c_void_p],
     "bspec_delta_recurrence": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gated_rmsnorm": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                            c_float, c_void_p],
+                            c_float, c_int, c_void_p],
     "bspec_rope_kv_append": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p],
     "bspec_rope_inplace": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_float,
@@ -184,12 +196,14 @@ def set_pdl(on: bool) -> None:
 
 _TRACE_SETTERS = ["bspec_trace_set_attention_tcgen05", "bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
                   "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05", "bspec_trace_set_latent",
-                  "bspec_trace_set_moe", "bspec_trace_set_latent_mma", "bspec_trace_set_delta"]
+                  "bspec_trace_set_moe", "bspec_trace_set_latent_mma", "bspec_trace_set_delta",
+                  "bspec_trace_set_state_mixers"]
 TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "silu_mul", 5: "rope_kv_append",
                       6: "rope_inplace", 7: "attn_generic", 8: "attn_decode", 9: "attn_prefill", 10: "sgemm",
                       11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 14: "add_layernorm", 15: "clamped_glu",
                       16: "gelu_erf", 17: "tanh_softcap", 18: "residual_update", 19: "qkv_prepare", 60: "delta_prepare",
-                      61: "delta_recurrence", 62: "gated_rmsnorm", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
+                      61: "delta_recurrence", 62: "gated_rmsnorm", 63: "bigram_add", 64: "scale", 65: "lightning_recurrence",
+                      66: "scan_conv", 67: "selective_scan", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
                       41: "latent_attn_generic", 42: "gate_heads", 43: "latent_attn_mma", 44: "latent_attn_join",
                       50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine", 55: "moe_skinny", 56: "moe_skinny_mma", 57: "moe_rank", 58: "moe_offsets", 59: "moe_place"}
 
@@ -267,38 +281,48 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: floa
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                out: torch.Tensor, delta_scale: float = 1.0, exact: bool = False) -> None:
-    """resid += delta_scale * delta (if given); out = the RMS-normalised rows times ``weight``.  ``exact``: the
+                out: torch.Tensor, delta_scale: float = 1.0, exact: bool = False,
+                delta_vec: Optional[torch.Tensor] = None) -> None:
+    """resid += delta_scale * delta_vec * delta (if delta is given; ``delta_vec`` float32 [d], a factor per column, or
+    None); out = the RMS-normalised rows times ``weight`` ([d], or one number for all columns).  ``exact``: the
     product with the weight is taken in float32 and the result rounded once; otherwise the normalised row is cast
     to the output type first and multiplied there."""
-    _require_cuda(resid, delta, weight, out)
+    _require_cuda(resid, delta, weight, out, delta_vec)
     assert resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous()
     n, d = resid.shape
-    assert out.shape == resid.shape and weight.numel() == d
+    assert out.shape == resid.shape and weight.numel() in (d, 1)
+    assert delta_vec is None or (delta_vec.dtype == torch.float32 and delta_vec.numel() == d and delta_vec.is_contiguous())
+    w_scalar = int(weight.numel() == 1 and d != 1)
     if delta is not None:
         assert delta.shape == resid.shape and delta.is_contiguous()
     dd = _dtype_code(delta.dtype) if delta is not None else _dtype_code(out.dtype)
     _check(load_library().bspec_add_rmsnorm(resid.data_ptr(), _ptr(delta), dd, weight.data_ptr(),
                                             _dtype_code(weight.dtype), out.data_ptr(), _dtype_code(out.dtype),
-                                            n, d, float(eps), float(delta_scale), int(bool(exact)), _stream()),
+                                            n, d, float(eps), float(delta_scale), int(bool(exact)), _ptr(delta_vec),
+                                            w_scalar, _stream()),
            "add_rmsnorm")
 
 
 def gather_rows_add(resid: torch.Tensor, pending: Optional[torch.Tensor], rows: torch.Tensor,
-                    out: torch.Tensor, scale: float = 1.0) -> None:
-    _require_cuda(resid, pending, rows, out)
+                    out: torch.Tensor, scale: float = 1.0, vec: Optional[torch.Tensor] = None) -> None:
+    """out[i] = resid[rows[i]] + scale * vec * pending[rows[i]] (``vec`` float32 [d], a factor per column, or None)."""
+    _require_cuda(resid, pending, rows, out, vec)
+    assert vec is None or (vec.dtype == torch.float32 and vec.numel() == out.shape[1] and vec.is_contiguous())
     assert resid.dtype == torch.float32 and out.dtype == torch.float32 and rows.dtype == torch.int32
     assert resid.is_contiguous() and out.is_contiguous() and (pending is None or pending.is_contiguous())
     pd = _dtype_code(pending.dtype) if pending is not None else F32
     _check(load_library().bspec_gather_rows_add(resid.data_ptr(), _ptr(pending), pd, rows.data_ptr(), out.data_ptr(),
-                                                out.shape[0], out.shape[1], resid.shape[0], float(scale), _stream()),
+                                                out.shape[0], out.shape[1], resid.shape[0], float(scale), _ptr(vec),
+                                                _stream()),
            "gather_rows_add")
 
 
 def residual_update(resid: torch.Tensor, pending: Optional[torch.Tensor], scale: float = 1.0,
-                    extra: Optional[torch.Tensor] = None) -> None:
-    """In place on the float32 residual: resid += scale * pending (if given) + extra (if given, float32)."""
-    _require_cuda(resid, pending, extra)
+                    extra: Optional[torch.Tensor] = None, vec: Optional[torch.Tensor] = None) -> None:
+    """In place on the float32 residual: resid += scale * vec * pending (if given; ``vec`` float32 [d], a factor per
+    column, or None) + extra (if given, float32)."""
+    _require_cuda(resid, pending, extra, vec)
+    assert vec is None or (vec.dtype == torch.float32 and vec.numel() == resid.shape[-1] and vec.is_contiguous())
     assert resid.dtype == torch.float32 and resid.is_contiguous()
     assert pending is None or (pending.shape == resid.shape and pending.is_contiguous())
     assert extra is None or (extra.shape == resid.shape and extra.is_contiguous() and extra.dtype == torch.float32)
@@ -306,7 +330,8 @@ def residual_update(resid: torch.Tensor, pending: Optional[torch.Tensor], scale:
         return
     _check(load_library().bspec_residual_update(resid.data_ptr(), _ptr(pending),
                                                 _dtype_code(pending.dtype) if pending is not None else F32,
-                                                float(scale), _ptr(extra), resid.numel(), _stream()), "residual_update")
+                                                float(scale), _ptr(extra), resid.numel(), _ptr(vec), resid.shape[-1],
+                                                _stream()), "residual_update")
 
 
 def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor,
@@ -372,6 +397,43 @@ def relu_mul(u: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
                                          _stream()), "relu_mul")
 
 
+def gelu_tanh_mul(u: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
+    """out = gelu(gate) * up with gelu(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); the column layouts of
+    ``silu_mul``."""
+    _require_cuda(u, out)
+    n, inter = out.shape
+    assert u.shape == (n, 2 * inter) and u.dtype == out.dtype and u.is_contiguous() and out.is_contiguous()
+    _check(load_library().bspec_gelu_tanh_mul(u.data_ptr(), out.data_ptr(), _dtype_code(u.dtype), n, inter, int(group),
+                                              _stream()), "gelu_tanh_mul")
+
+
+GATED_ACTIVATIONS = {"silu": (1, silu_mul), "relu": (3, relu_mul), "gelu_tanh": (4, gelu_tanh_mul)}   # epilogue kind, kernel
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """In place on float32: x *= factor."""
+    _require_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(load_library().bspec_scale(x.data_ptr(), x.numel(), float(factor), _stream()), "scale")
+    return x
+
+
+def bigram_add(resid: torch.Tensor, table: torch.Tensor, prev: torch.Tensor, ctx, buckets: int, mul_prev: int,
+               mul_cur: int, vocab: int) -> None:
+    """resid[t] += table[(previous token * mul_prev + token * mul_cur) mod buckets], and table[buckets] for the token
+    at position 0.  ``prev`` int32 [slots, >= 1]: the last token of every request's earlier steps; it is read for a
+    portion's first token and then set to the portion's last token."""
+    _require_cuda(resid, table, prev)
+    n, d = resid.shape
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and table.is_contiguous()
+    assert table.shape == (buckets + 1, d) and prev.dtype == torch.int32 and prev.stride(-1) == 1
+    _check(load_library().bspec_bigram_add(resid.data_ptr(), ctx.token_ids.data_ptr(), ctx.positions.data_ptr(),
+                                           ctx.tok_entry.data_ptr(), ctx.qo_indptr.data_ptr(),
+                                           ctx.state_slots.data_ptr(), prev.data_ptr(), prev.stride(0),
+                                           table.data_ptr(), _dtype_code(table.dtype), n, d, int(vocab), int(buckets),
+                                           int(mul_prev), int(mul_cur), _stream()), "bigram_add")
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GLU_GROUP) -> torch.Tensor:
     """[I, d] gate and up rows -> [2I, d] in blocks of ``group`` gate rows followed by their up rows."""
     inter, d = gate.shape
@@ -380,10 +442,10 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GLU_GR
 
 
 def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP, activation: str = "silu") -> torch.Tensor:
-    """act(x Wg^T) * (x Wu^T), act = silu or relu, for bfloat16 with ``w13`` interleaved by ``interleave_gate_up``:
-    one kernel with the activation in the GEMM's epilogue for decode-sized steps, vendor GEMM + activation kernel
-    otherwise."""
-    assert activation in ("silu", "relu")
+    """act(x Wg^T) * (x Wu^T), act = silu, relu or gelu_tanh, for bfloat16 with ``w13`` interleaved by
+    ``interleave_gate_up``: one kernel with the activation in the GEMM's epilogue for decode-sized steps, vendor GEMM +
+    activation kernel otherwise."""
+    epilogue, kernel = GATED_ACTIVATIONS[activation]
     _require_cuda(x, w13)
     M, K = x.shape
     N = w13.shape[0]
@@ -392,12 +454,12 @@ def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP, activ
             and x.is_contiguous() and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
         out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
         _check(load_library().bspec_gemm_tc(x.data_ptr(), w13.data_ptr(), out.data_ptr(), M, N, K, 0,
-                                            3 if activation == "relu" else 1,
+                                            epilogue,
                                             _status_word(x.device).data_ptr(), sm_count(x.device), _stream()), "gemm_tc_glu")
         return out
     u = linear(x, w13)
     out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
-    (relu_mul if activation == "relu" else silu_mul)(u, out, group)
+    kernel(u, out, group)
     return out
 
 
@@ -623,7 +685,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(qkv.dtype),
         ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
         ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, head_dim, tables.page_size, float(scale),
-        int(window), int(chunk), _ptr(sink), cache.shape[0], _stream()), "attention_generic")
+        int(window), int(chunk), _ptr(sink), cache.shape[0], 0.0, 0, None, 0, out.stride(0), 1.0, _stream()),
+        "attention_generic")
 
 
 def qkv_prepare(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, v_dim: int,
@@ -634,10 +697,12 @@ def qkv_prepare(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
     """From the float32 rows [q | k | v] of the fused projection: bias, rotation of the first ``rotary_dim`` numbers
     of every q and k head (cosine and sine times ``magnitude``), division of every q and k head by its root mean
     square (``norm_eps`` > 0), in float32; returns q [n, n_heads * head_dim] in the cache's dtype and writes k and v
-    into the cache page of each token's position.  Page layout: [k: kv head, row, head_dim | v: kv head, row, v_dim]."""
+    into the cache page of each token's position.  Page layout: [k: kv head, row, head_dim | v: kv head, row, v_dim].
+    ``qkv`` may be a view of the leading columns of wider rows.  ``v_dim`` 0: no values (the keys serve as values)
+    and a page holds keys only."""
     _require_cuda(qkv, cache, positions)
     n = qkv.shape[0]
-    assert qkv.dtype == torch.float32 and qkv.is_contiguous() and cache.is_contiguous()
+    assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and cache.is_contiguous()
     assert qkv.shape[1] == (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_dim
     assert positions.dtype == torch.int32 and tok_entry.dtype == torch.int32
     if bias is not None:
@@ -646,7 +711,7 @@ def qkv_prepare(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
         assert inv_freq.dtype == torch.float32 and inv_freq.shape == (2, rotary_dim // 2) and inv_freq.is_contiguous()
     q = torch.empty((n, n_heads * head_dim), dtype=cache.dtype, device=qkv.device)
     _check(load_library().bspec_qkv_prepare(
-        qkv.data_ptr(), n, n_heads, n_kv_heads, head_dim, v_dim, _ptr(bias),
+        qkv.data_ptr(), qkv.stride(0), n, n_heads, n_kv_heads, head_dim, v_dim, _ptr(bias),
         _dtype_code(bias.dtype) if bias is not None else F32, _ptr(inv_freq), int(rotary_dim), int(bool(interleaved)),
         float(magnitude), float(norm_eps), positions.data_ptr(), tok_entry.data_ptr(), kv_indptr.data_ptr(),
         kv_indices.data_ptr(), q.data_ptr(), cache.data_ptr(), _dtype_code(cache.dtype), int(page_size),
@@ -656,19 +721,25 @@ def qkv_prepare(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
 
 def masked_attention(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables, n_heads: int,
                      n_kv_heads: int, head_dim: int, v_dim: int, scale: float, window: int = 0, chunk: int = 0,
-                     sink: Optional[torch.Tensor] = None) -> None:
+                     sink: Optional[torch.Tensor] = None, softcap: float = 0.0, values_are_keys: bool = False,
+                     gate: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
     """Causal attention with optional masks and sink over pages laid out [k | v] with values of size ``v_dim``:
     ``window`` > 0 keeps the last ``window`` keys, ``chunk`` > 0 the keys of the query's own chunk of positions;
-    ``sink`` (float32 per query head) adds exp(sink) to the softmax denominator.  float32 arithmetic."""
-    _require_cuda(q, out, cache, sink)
-    assert q.stride(1) == 1 and out.is_contiguous() and out.dtype == q.dtype == cache.dtype
-    assert out.shape == (q.shape[0], n_heads * v_dim)
+    ``sink`` (float32 per query head) adds exp(sink) to the softmax denominator; ``softcap`` c > 0 turns a scaled
+    score s into c tanh(s / c); ``values_are_keys``: pages hold keys only and a key is its own value;  ``gate``
+    (a float32 view [n, n_heads * v_dim] of rows that may be wider): the output is multiplied by sigmoid(gate);
+    ``out_scale`` multiplies it.  ``out`` may be a view of the leading columns of wider rows.  float32 arithmetic."""
+    _require_cuda(q, out, cache, sink, gate)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == q.dtype == cache.dtype
+    assert out.shape == (q.shape[0], n_heads * v_dim) and (not values_are_keys or v_dim == head_dim)
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous())
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape == out.shape and gate.stride(1) == 1)
     _check(load_library().bspec_attention_masked(
         q.data_ptr(), q.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(q.dtype), ctx.qo_indptr.data_ptr(),
         ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(), ctx.n_entries,
         ctx.max_q_len, n_heads, n_kv_heads, head_dim, v_dim, tables.page_size, float(scale), int(window), int(chunk),
-        _ptr(sink), cache.shape[0], _stream()), "attention_masked")
+        _ptr(sink), cache.shape[0], float(softcap), int(bool(values_are_keys)), _ptr(gate),
+        gate.stride(0) if gate is not None else 0, out.stride(0), float(out_scale), _stream()), "attention_masked")
 
 
 # ---------------------------------------------------------------------------- gated delta rule
@@ -715,9 +786,11 @@ def delta_recurrence(mix: torch.Tensor, gates: torch.Tensor, proj: torch.Tensor,
 
 
 def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, n_heads: int, v_dim: int,
-                  out_dtype: torch.dtype) -> torch.Tensor:
+                  out_dtype: torch.dtype, gate_act: str = "silu") -> torch.Tensor:
     """o float32 [n, H * V]; gate a float32 view [n, H * V] of rows that may be wider.  Returns
-    o / rms_V(o) * weight * silu(gate) in ``out_dtype``."""
+    o / rms_V(o) * weight * act(gate) in ``out_dtype``, act = "silu" or "sigmoid".  With H = 1 the norm runs over the
+    whole row."""
+    assert gate_act in ("silu", "sigmoid")
     _require_cuda(o, gate, weight)
     n = o.shape[0]
     assert o.dtype == torch.float32 and o.is_contiguous() and gate.dtype == torch.float32 and gate.stride(1) == 1
@@ -725,8 +798,77 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
     out = torch.empty((n, n_heads * v_dim), dtype=out_dtype, device=o.device)
     _check(load_library().bspec_gated_rmsnorm(o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(),
                                               _dtype_code(weight.dtype), out.data_ptr(), _dtype_code(out_dtype), n,
-                                              n_heads, v_dim, float(eps), _stream()), "gated_rmsnorm")
+                                              n_heads, v_dim, float(eps), int(gate_act == "sigmoid"), _stream()),
+           "gated_rmsnorm")
     return out
+
+
+# ---------------------------------------------------------------------------- lightning attention, selective scan
+
+def lightning_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor,
+                         state: torch.Tensor, ctx, n_heads: int, dim: int, v_dim: int) -> torch.Tensor:
+    """Linear attention with a fixed decay per head over every entry's portion: S <- decay_h S + k v^T, o = S^T q, with
+    q, k, v = silu of the float32 columns of ``proj`` at ``q_off`` / ``k_off`` (H * dim each) and ``v_off`` (H * v_dim).
+    ``state[slot]`` holds S as [head, value column, key row] float32 and is read and written.  Returns o float32
+    [n, H * v_dim]."""
+    _require_cuda(proj, decay, state)
+    n, ld = proj.shape
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and state.dtype == torch.float32 and state.stride(1) == 1
+    assert decay.dtype == torch.float32 and decay.numel() == n_heads and decay.is_contiguous()
+    assert state.shape[1] >= n_heads * v_dim * dim and dim <= 256
+    assert max(q_off, k_off) + n_heads * dim <= ld and v_off + n_heads * v_dim <= ld
+    out = torch.empty((n, n_heads * v_dim), dtype=torch.float32, device=proj.device)
+    _check(load_library().bspec_lightning_recurrence(
+        proj.data_ptr(), proj.stride(0), int(q_off), int(k_off), int(v_off), decay.data_ptr(), state.data_ptr(),
+        state.stride(0), ctx.qo_indptr.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(), ctx.n_entries, n_heads,
+        dim, v_dim, _stream()), "lightning_recurrence")
+    return out
+
+
+def scan_conv(xz: torch.Tensor, conv: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, tail_off: int, ctx,
+              inner: int, taps: int, run_dtype: torch.dtype):
+    """silu(bias + causal convolution over ``taps`` inputs) of the first ``inner`` float32 columns of ``xz``, per
+    channel; inputs before a portion come from ``state[slot, tail_off:]`` ([(taps-1), inner], oldest first).  Returns
+    the result as float32 [n, inner] and in ``run_dtype`` (the same tensor when that is float32)."""
+    _require_cuda(xz, conv, bias, state)
+    n = xz.shape[0]
+    assert xz.dtype == torch.float32 and xz.stride(1) == 1 and xz.shape[1] >= inner
+    assert conv.shape == (inner, taps) and conv.is_contiguous() and bias.numel() == inner and conv.dtype == bias.dtype
+    assert state.dtype == torch.float32 and tail_off + (taps - 1) * inner <= state.shape[1]
+    xc = torch.empty((n, inner), dtype=torch.float32, device=xz.device)
+    xr = xc if run_dtype == torch.float32 else torch.empty((n, inner), dtype=run_dtype, device=xz.device)
+    _check(load_library().bspec_scan_conv(
+        xz.data_ptr(), xz.stride(0), conv.data_ptr(), bias.data_ptr(), _dtype_code(conv.dtype), state.data_ptr(),
+        state.stride(0), int(tail_off), ctx.qo_indptr.data_ptr(), ctx.tok_entry.data_ptr(), ctx.state_slots.data_ptr(),
+        xc.data_ptr(), None if xr is xc else xr.data_ptr(), _dtype_code(run_dtype), n, inner, taps, _stream()),
+        "scan_conv")
+    return xc, xr
+
+
+def selective_scan(xz: torch.Tensor, xc: torch.Tensor, dt_raw: torch.Tensor, bc: torch.Tensor, a_log: torch.Tensor,
+                   d_skip: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, tail_off: int, ctx,
+                   out: torch.Tensor, out_scale: float, inner: int, n_state: int, taps: int) -> None:
+    """The selective scan over every entry's portion.  Per channel c and state n, with dt = softplus(dt_raw + dt_bias)
+    and A = -exp(a_log): S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n; y_c = sum_n S[c, n] C_n + D_c x_c;
+    out[t, c] = y_c silu(z_c) out_scale.  ``xz`` float32 [n, >= 2 inner] = [x before the convolution | z]; ``xc``
+    float32 [n, inner] after it; ``bc`` float32 [n, 2 N] = [B | C]; ``state[slot]`` = [S as [N, inner] | the
+    convolution's last taps-1 inputs at ``tail_off``], read and written.  ``out``: a view [n, inner] of rows that may
+    be wider, float32 or bfloat16."""
+    _require_cuda(xz, xc, dt_raw, bc, a_log, d_skip, dt_bias, state, out)
+    n = xz.shape[0]
+    f32 = torch.float32
+    assert xz.dtype == f32 and xz.stride(1) == 1 and xz.shape[1] >= 2 * inner
+    assert xc.dtype == f32 and xc.is_contiguous() and xc.shape == (n, inner)
+    assert dt_raw.dtype == f32 and dt_raw.is_contiguous() and dt_raw.shape == (n, inner)
+    assert bc.dtype == f32 and bc.stride(1) == 1 and bc.shape == (n, 2 * n_state)
+    assert a_log.shape == (inner, n_state) and a_log.is_contiguous() and a_log.dtype == d_skip.dtype == dt_bias.dtype
+    assert state.dtype == f32 and tail_off >= n_state * inner and tail_off + (taps - 1) * inner <= state.shape[1]
+    assert out.shape == (n, inner) and out.stride(1) == 1
+    _check(load_library().bspec_selective_scan(
+        xz.data_ptr(), xz.stride(0), xc.data_ptr(), dt_raw.data_ptr(), bc.data_ptr(), bc.stride(0), a_log.data_ptr(),
+        d_skip.data_ptr(), dt_bias.data_ptr(), _dtype_code(a_log.dtype), state.data_ptr(), state.stride(0),
+        int(tail_off), ctx.qo_indptr.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(), _dtype_code(out.dtype),
+        out.stride(0), float(out_scale), ctx.n_entries, inner, n_state, taps, _stream()), "selective_scan")
 
 
 # ---------------------------------------------------------------------------- matrix products
@@ -772,7 +914,7 @@ def check_status() -> None:
     check_bounds()
 
 
-_BOUNDS_REPORTS = ["bspec_bounds_report_elementwise", "bspec_bounds_report_gemm_tcgen05",
+_BOUNDS_REPORTS = ["bspec_bounds_report_state_mixers", "bspec_bounds_report_elementwise", "bspec_bounds_report_gemm_tcgen05",
                    "bspec_bounds_report_attention_generic", "bspec_bounds_report_attention_bf16",
                    "bspec_bounds_report_latent", "bspec_bounds_report_latent_mma", "bspec_bounds_report_delta"]
 BOUNDS_CODES = {101: "token id (embedding)", 102: "row (gather)", 103: "block-table slot (rotary + cache append)",

@@ -12,6 +12,7 @@ from ..parts.base import Runtime
 from .decoder import CacheNeed, DecoderModel, LayerCache
 from .llama import build_llama
 from .lupusun import build_lupusun
+from .tokolorn import build_tokolorn
 from .spec import LayerSpec, ModelSpec, RunEntry, prenorm_layer
 from .vabanex import build_vabanex
 
@@ -32,6 +33,7 @@ def get_model(config, runtime: Runtime) -> DecoderModel:
 register_model("LlamaForCausalLM", build_llama)
 register_model("Vabanex", build_vabanex)
 register_model("Lupusun", build_lupusun)
+register_model("Tokolorn", build_tokolorn)
 
 __all__ = ["MODEL_REGISTRY", "register_model", "get_model", "DecoderModel", "LayerCache", "CacheNeed",
-           "ModelSpec", "LayerSpec", "RunEntry", "prenorm_layer", "build_llama", "build_lupusun", "build_vabanex"]
+           "ModelSpec", "LayerSpec", "RunEntry", "prenorm_layer", "build_llama", "build_lupusun", "build_tokolorn", "build_vabanex"]

@@ -65,6 +65,7 @@ class DecoderModel:
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.caches: List[Optional[LayerCache]] = [None] * len(spec.order)
+        self.input_state: Optional[torch.Tensor] = None      # the input part's per-request state, if it declared one
         # debugging aid: called as probe(run index, residual after the run, float32 [n, d]) when set
         self.layer_probe = None
 
@@ -111,16 +112,24 @@ class DecoderModel:
 
     # -- cache -----------------------------------------------------------------
     def cache_needs(self) -> List[CacheNeed]:
+        """One need per run of the order; after them one more (state only) if the input part keeps something per
+        request."""
         out = []
         for run in self.spec.order:
             block = self.blocks[run.layer]
             mixer = getattr(block, block.MIXER_SLOT)
             out.append(CacheNeed(mixer.cache_spec(), mixer.state_spec(), run.cache_from))
+        input_state = self.input_part.state_spec() if self.input_part is not None else None
+        if input_state is not None:
+            out.append(CacheNeed(None, input_state, None))
         return out
 
     def attach_caches(self, caches: List[Optional[LayerCache]]) -> None:
-        assert len(caches) == len(self.spec.order)
-        self.caches = list(caches)
+        n = len(self.spec.order)
+        assert len(caches) in (n, n + 1)
+        self.caches = list(caches[:n])
+        extra = caches[n] if len(caches) > n else None
+        self.input_state = extra.state if extra is not None else None
 
     # -- one step --------------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor:
@@ -132,28 +141,33 @@ class DecoderModel:
         with bucket("embed"):
             ops.embed(ctx.token_ids, self.embed, resid, s.embed_scale)
         if self.input_part is not None:
-            self.input_part.forward(resid, ctx)
+            if self.input_state is not None:
+                self.input_part.forward(resid, ctx, self.input_state)
+            else:
+                self.input_part.forward(resid, ctx)
         first = resid.clone() if any(run.add_input for run in s.order) else None
-        pending, scale = None, 1.0
+        pending, scale, vec = None, 1.0, None
         for e, run in enumerate(s.order):
             if run.add_input:
-                ops.residual_update(resid, pending, scale, first)
-                pending, scale = None, 1.0
+                ops.residual_update(resid, pending, scale, first, vec)
+                pending, scale, vec = None, 1.0, None
             block = self.blocks[run.layer]
             # a block whose forward knows no branch factors (one registered from outside) can follow any block that
             # leaves its branch unscaled
             extra = {} if scale == 1.0 else {"pending_scale": scale}
+            if vec is not None:
+                extra["pending_vec"] = vec
             resid, pending = block.forward(resid, pending, ctx, self.caches[e], **extra)
-            scale = getattr(block, "residual_mult", 1.0)
+            scale, vec = getattr(block, "residual_mult", 1.0), getattr(block, "residual_vec", None)
             if self.layer_probe is not None:
                 after = resid.clone()
-                ops.residual_update(after, pending, scale)
+                ops.residual_update(after, pending, scale, vec=vec)
                 self.layer_probe(e, after)
         n_out = ctx.n_logit_rows
         if n_out == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.runtime.device)
         picked = torch.empty((n_out, s.hidden_size), dtype=torch.float32, device=self.runtime.device)
-        ops.gather_rows_add(resid, pending, ctx.logit_rows, picked, scale)
+        ops.gather_rows_add(resid, pending, ctx.logit_rows, picked, scale, vec)
         z = self.final_norm.forward(picked, None)
         with bucket("lm_head"):
             logits = ops.linear(z, self.head, out_dtype=torch.float32)

@@ -1,8 +1,9 @@
-from .base import (BLOCKS, FEED_FORWARDS, INPUT_PARTS, LOGITS_PARTS, MIXERS, NORMS, POSITION_ENCODINGS, Block, CacheSpec,
+from .base import (BLOCKS, BRANCH_SCALES, FEED_FORWARDS, INPUT_PARTS, LOGITS_PARTS, MIXERS, NORMS, POSITION_ENCODINGS, Block, CacheSpec,
                    FeedForward, InputPart, LogitsPart, Mixer, Norm, ParamSpec, Part, PartSpec, PositionEncoding, Runtime,
                    StateSpec, build_part, register_part)
-from . import attention, block, delta_rule, latent_attention, logits, mlp, moe, norm, rope, sink_attention  # noqa: F401  (registers the built-in parts)
+from . import (attention, block, delta_rule, embedding, latent_attention, lightning, logits, mlp, moe, norm, parallel, rope,
+               selective_scan, sink_attention)  # noqa: F401  (registers the built-in parts)
 
-__all__ = ["BLOCKS", "FEED_FORWARDS", "INPUT_PARTS", "LOGITS_PARTS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block",
+__all__ = ["BLOCKS", "BRANCH_SCALES", "FEED_FORWARDS", "INPUT_PARTS", "LOGITS_PARTS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block",
            "CacheSpec", "FeedForward", "InputPart", "LogitsPart", "Mixer", "Norm", "ParamSpec", "Part", "PartSpec", "PositionEncoding", "Runtime", "StateSpec",
            "build_part", "register_part"]

@@ -9,7 +9,7 @@ checkpoint names.  The reference fixes the parts by subclass hooks
 one model may mix different mixers and feed-forwards.
 
 Registries: ``MIXERS``, ``FEED_FORWARDS``, ``NORMS``, ``POSITION_ENCODINGS``,
-``BLOCKS``, ``INPUT_PARTS``, ``LOGITS_PARTS``.  ``register_part(registry, kind)``
+``BLOCKS``, ``BRANCH_SCALES``, ``INPUT_PARTS``, ``LOGITS_PARTS``.  ``register_part(registry, kind)``
 is a class decorator; ``build_part(registry, spec, runtime)`` instantiates
 ``spec.kind`` with ``spec.params``.
 """
@@ -98,12 +98,14 @@ class Part:
 
 
 class Norm(Part):
-    """``forward(resid, delta, delta_scale=1.0)``: ``resid`` is the float32 residual
-    stream [n, d]; if ``delta`` is given, ``delta_scale * delta`` is first added into
+    """``forward(resid, delta, delta_scale=1.0, delta_vec=None)``: ``resid`` is the float32 residual
+    stream [n, d]; if ``delta`` is given, ``delta_scale * delta`` (times ``delta_vec``, a float32 factor per
+    column, when a block scales its branches that way) is first added into
     ``resid`` in place (the residual sum, in 32-bit); returns the normalised rows in
     the run dtype."""
 
-    def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], delta_scale: float = 1.0) -> torch.Tensor:
+    def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], delta_scale: float = 1.0,
+                delta_vec: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -149,9 +151,14 @@ class FeedForward(Part):
 class InputPart(Part):
     """Runs once per step right after the embedding: ``forward(resid, ctx)`` changes
     the float32 residual rows [n, d] in place (a learned absolute position row
-    added to each token, a multiplier ...)."""
+    added to each token, a multiplier ...).  A part that keeps something per request from step to step (the
+    request's last token, say) declares it with ``state_spec()`` and receives the tensor [slots, *shape] as
+    ``state``; it is zeroed when a request is admitted and indexed by ``ctx.state_slots``."""
 
-    def forward(self, resid: torch.Tensor, ctx) -> None:
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, resid: torch.Tensor, ctx, state: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
 
 
@@ -168,6 +175,7 @@ FEED_FORWARDS: Dict[str, type] = {}
 NORMS: Dict[str, type] = {}
 POSITION_ENCODINGS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
+BRANCH_SCALES: Dict[str, type] = {}
 INPUT_PARTS: Dict[str, type] = {}
 LOGITS_PARTS: Dict[str, type] = {}
 
@@ -184,10 +192,13 @@ class Block:
     ``forward(resid, pending, ctx, cache, pending_scale=1.0)`` takes the float32 residual and a
     not-yet-added branch output (or None) with the factor it is to be added with, and returns the
     residual and its own last branch output, so the add can be fused into the next norm.  ``residual_mult``
-    is the factor of the branch a block returns."""
+    is the factor of the branch a block returns; a block that also multiplies that branch by a learned factor per
+    column has it (float32 [d]) in ``residual_vec``, and whoever adds the branch applies both (the next block gets
+    the vector as ``pending_vec``)."""
     SLOTS: Dict[str, Dict[str, type]] = {}
     MIXER_SLOT = "mixer"
     residual_mult = 1.0
+    residual_vec = None
 
     def __init__(self, **parts):
         missing, extra = set(self.SLOTS) - set(parts), set(parts) - set(self.SLOTS)

@@ -5,7 +5,11 @@ stream itself is float32.  A block returns its last branch unscaled; ``residual_
 multiplies it by (the next block gets it as ``pending_scale``)."""
 from __future__ import annotations
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, register_part
+from typing import Dict
+
+import torch
+
+from .base import BLOCKS, BRANCH_SCALES, FEED_FORWARDS, MIXERS, NORMS, Block, ParamSpec, Part, Runtime, register_part
 
 
 @register_part(BLOCKS, "prenorm")
@@ -16,8 +20,8 @@ class PreNormBlock(Block):
         super().__init__(**parts)
         self.residual_mult = float(residual_mult)
 
-    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0):
-        a = self.norm1.forward(resid, pending, pending_scale)
+    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0, pending_vec=None):
+        a = self.norm1.forward(resid, pending, pending_scale, pending_vec)
         y = self.mixer.forward(a, ctx, cache)
         f = self.norm2.forward(resid, y, self.residual_mult)
         return resid, self.ffn.forward(f, ctx)
@@ -32,6 +36,55 @@ class PreNormMixerBlock(Block):
         super().__init__(**parts)
         self.residual_mult = float(residual_mult)
 
-    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0):
-        a = self.norm1.forward(resid, pending, pending_scale)
+    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0, pending_vec=None):
+        a = self.norm1.forward(resid, pending, pending_scale, pending_vec)
+        return resid, self.mixer.forward(a, ctx, cache)
+
+
+@register_part(BRANCH_SCALES, "channel")
+class ChannelScale(Part):
+    """A learned factor per column on a branch's output before it joins the residual stream (layer scale).  Held in
+    float32: the product and the sum are taken there."""
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, dim: int):
+        self.runtime, self.dim = runtime, int(dim)
+        self.weight = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((self.dim,), role="vector", init="ones_normal")}
+
+    def bind(self, params):
+        self.weight = params["weight"].to(torch.float32).contiguous()
+
+
+@register_part(BLOCKS, "prenorm_scaled")
+class ScaledPreNormBlock(Block):
+    """Pre-norm layer whose branches are multiplied column by column by learned vectors before the residual sum:
+    h = x + s1 * mixer(norm1(x));  x' = h + s2 * ffn(norm2(h))."""
+    SLOTS = {"norm1": NORMS, "mixer": MIXERS, "scale1": BRANCH_SCALES, "norm2": NORMS, "ffn": FEED_FORWARDS,
+             "scale2": BRANCH_SCALES}
+
+    @property
+    def residual_vec(self):
+        return self.scale2.weight
+
+    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0, pending_vec=None):
+        a = self.norm1.forward(resid, pending, pending_scale, pending_vec)
+        y = self.mixer.forward(a, ctx, cache)
+        f = self.norm2.forward(resid, y, 1.0, self.scale1.weight)
+        return resid, self.ffn.forward(f, ctx)
+
+
+@register_part(BLOCKS, "prenorm_mixer_scaled")
+class ScaledPreNormMixerBlock(Block):
+    """The same without a feed-forward: x' = x + s1 * mixer(norm1(x))."""
+    SLOTS = {"norm1": NORMS, "mixer": MIXERS, "scale1": BRANCH_SCALES}
+
+    @property
+    def residual_vec(self):
+        return self.scale1.weight
+
+    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0, pending_vec=None):
+        a = self.norm1.forward(resid, pending, pending_scale, pending_vec)
         return resid, self.mixer.forward(a, ctx, cache)

@@ -17,3 +17,16 @@ class TanhSoftCap(LogitsPart):
 
     def forward(self, logits, ctx) -> None:
         ops.tanh_softcap_(logits, self.cap)
+
+
+@register_part(LOGITS_PARTS, "scale")
+class LogitScale(LogitsPart):
+    """logits <- factor * logits, in place on the float32 logits."""
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, factor: float):
+        self.runtime, self.factor = runtime, float(factor)
+
+    def forward(self, logits, ctx) -> None:
+        if self.factor != 1.0:
+            ops.scale_(logits, self.factor)

@@ -15,12 +15,13 @@ from .base import FEED_FORWARDS, FeedForward, ParamSpec, Runtime, register_part
 
 @register_part(FEED_FORWARDS, "swiglu")
 class SwiGLU(FeedForward):
-    """``activation``: what the gate passes through, "silu" (the reference's) or "relu"."""
+    """``activation``: what the gate passes through, "silu" (the reference's), "relu" or "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
     graph_safe = True
     def __init__(self, runtime: Runtime, dim: int, intermediate: int, activation: str = "silu"):
         self.runtime, self.dim, self.intermediate = runtime, int(dim), int(intermediate)
-        if activation not in ("silu", "relu"):
-            raise ValueError(f"gated feed-forward activation {activation!r} is not known ('silu', 'relu')")
+        if activation not in ops.GATED_ACTIVATIONS:
+            raise ValueError(f"gated feed-forward activation {activation!r} is not known ({sorted(ops.GATED_ACTIVATIONS)})")
         self.activation = activation
         self.w13 = self.w2 = None
 
@@ -49,7 +50,7 @@ class SwiGLU(FeedForward):
                 u = ops.linear(x, self.w13)
             m = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
             with bucket("mlp.act"):
-                (ops.relu_mul if self.activation == "relu" else ops.silu_mul)(u, m)
+                ops.GATED_ACTIVATIONS[self.activation][1](u, m)
         with bucket("mlp.down_proj"):
             return ops.linear(m, self.w2)
 

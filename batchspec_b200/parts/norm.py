@@ -16,21 +16,24 @@ from .base import INPUT_PARTS, NORMS, InputPart, Norm, ParamSpec, Runtime, regis
 @register_part(NORMS, "rmsnorm")
 class RMSNorm(Norm):
     graph_safe = True
-    def __init__(self, runtime: Runtime, dim: int, eps: float, single_rounding: bool = False):
+    def __init__(self, runtime: Runtime, dim: int, eps: float, single_rounding: bool = False,
+                 scalar_weight: bool = False):
+        """``scalar_weight``: the weight is one number (a tensor without dimensions) for all coordinates."""
         self.runtime, self.dim, self.eps = runtime, int(dim), float(eps)
         self.single_rounding = bool(single_rounding)
+        self.scalar_weight = bool(scalar_weight)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.dim,), role="vector", init="ones_normal")}
+        return {"weight": ParamSpec(() if self.scalar_weight else (self.dim,), role="vector", init="ones_normal")}
 
     def bind(self, params):
-        self.weight = params["weight"]
+        self.weight = params["weight"].reshape(1).contiguous() if self.scalar_weight else params["weight"]
 
-    def forward(self, resid, delta=None, delta_scale: float = 1.0):
+    def forward(self, resid, delta=None, delta_scale: float = 1.0, delta_vec=None):
         out = torch.empty(resid.shape, dtype=self.runtime.dtype, device=resid.device)
         with bucket("norm"):
-            ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, delta_scale, self.single_rounding)
+            ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, delta_scale, self.single_rounding, delta_vec)
         return out
 
 
@@ -54,9 +57,9 @@ class LayerNorm(Norm):
         if self.bias.dtype != self.weight.dtype:
             self.bias = self.bias.to(self.weight.dtype)
 
-    def forward(self, resid, delta=None, delta_scale: float = 1.0):
-        if delta is not None and delta_scale != 1.0:
-            ops.residual_update(resid, delta, delta_scale)
+    def forward(self, resid, delta=None, delta_scale: float = 1.0, delta_vec=None):
+        if delta is not None and (delta_scale != 1.0 or delta_vec is not None):
+            ops.residual_update(resid, delta, delta_scale, vec=delta_vec)
             delta = None
         out = torch.empty(resid.shape, dtype=self.runtime.dtype, device=resid.device)
         with bucket("norm"):
@@ -79,7 +82,7 @@ class InputRMSNorm(InputPart):
     def bind(self, params):
         self.weight = params["weight"]
 
-    def forward(self, resid, ctx) -> None:
+    def forward(self, resid, ctx, state=None) -> None:
         out = torch.empty_like(resid)
         with bucket("norm"):
             ops.add_rmsnorm(resid, None, self.weight, self.eps, out, 1.0, True)
