@@ -116,12 +116,24 @@ __device__ __forceinline__ void load_q_tile(__nv_bfloat16* Qs, const __nv_bfloat
   }
 }
 
+// A raw score in base-2 units: s * scale * log2(e), or with a soft cap c > 0: c tanh(s * scale / c) * log2(e).
+__device__ __forceinline__ float score2(float s, float scale_log2, float softcap) {
+  if (softcap > 0.f) {
+    // tanh(x) = 1 - 2 / (1 + e^(2x)) with the float32 exponential and a float32 division (tanh.approx has 11 good
+    // bits, less than a float32 score asks for); e^(2x) = inf gives 1, 0 gives -1
+    const float x2 = s * scale_log2 * (2.f / softcap);   // 2x in base-2 units
+    const float t = 1.f - __fdividef(2.f, 1.f + exp2f(x2));
+    return softcap * 1.4426950408889634f * t;
+  }
+  return s * scale_log2;
+}
+
 // One warp: scores of its 16 rows against 16 keys (kb .. kb+15 of the tile), online softmax, P*V.
 // qf: A fragments of the rows for every 16-dim step.  Row state (m, l) per thread for rows lane/4 and lane/4+8.
 template <int HD, bool TMA_TILE = false>
 __device__ __forceinline__ void block16(const uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* Ks,
                                         const __nv_bfloat16* Vs, int kb, int key0, int row_lim0, int row_lim1,
-                                        int row_lo0, int row_lo1, int k_end, float scale_log2, float (&m)[2],
+                                        int row_lo0, int row_lo1, int k_end, float scale_log2, float softcap, float (&m)[2],
                                         float (&l)[2], float (&o)[HD / 8][4]) {
   const int lane = threadIdx.x & 31;
   float s[2][4];
@@ -146,7 +158,7 @@ __device__ __forceinline__ void block16(const uint32_t (&qf)[HD / 16][4], const 
       const int key = key0 + kb + 8 * nt + 2 * (lane & 3) + (i & 1);
       const int lim = (i >> 1) ? row_lim1 : row_lim0, lo = (i >> 1) ? row_lo1 : row_lo0;
       const bool ok = key <= lim && key >= lo && key < k_end;
-      s[nt][i] = ok ? s[nt][i] * scale_log2 : -INFINITY;
+      s[nt][i] = ok ? score2(s[nt][i], scale_log2, softcap) : -INFINITY;
       mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
     }
   float corr[2], msafe[2];
@@ -318,7 +330,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
                    float* __restrict__ o_part, float* __restrict__ ml_part, int* __restrict__ tile_counters,
                    const __nv_bfloat16* __restrict__ cache, const int* __restrict__ qo_indptr,
                    const int* __restrict__ positions, const int* __restrict__ kv_indptr,
-                   const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
+                   const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, float softcap, int window,
                    int n_splits, int row_tiles, int max_q_short, long long n_pages,
                     const float* __restrict__ sink_l2) {
   bspec::pdl_prologue(8);
@@ -398,7 +410,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
       __syncthreads();
       const int key0 = k_begin + it * KT;
       if (key0 + 16 * warp < k_end)
-        block16<HD>(qf, Ks, Vs, 16 * warp, key0, lim[0], lim[1], lo[0], lo[1], k_end, scale_log2, m, l, o);
+        block16<HD>(qf, Ks, Vs, 16 * warp, key0, lim[0], lim[1], lo[0], lo[1], k_end, scale_log2, softcap, m, l, o);
       __syncthreads();
     }
   }
@@ -423,7 +435,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
                        float* __restrict__ ml_part, int* __restrict__ tile_counters, int* __restrict__ status,
                        const int* __restrict__ qo_indptr, const int* __restrict__ positions,
                        const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
-                       int page_size, float scale_log2, int window, int n_splits, int row_tiles, int max_q_short,
+                       int page_size, float scale_log2, float softcap, int window, int n_splits, int row_tiles, int max_q_short,
                     const float* __restrict__ sink_l2) {
   // The step's metadata (lengths, positions, block tables) was uploaded before the step's first kernel, and every
   // cached key below the first new token was written by earlier steps: the producer may fetch those tiles while
@@ -549,7 +561,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       const int key0 = k_begin + it * KT;
       if (key0 + 16 * warp < k_end)
         block16<HD, true>(qf, Ks, Ks + TILE_ELEMS, 16 * warp, key0, lim[0], lim[1], lo[0], lo[1], k_end, scale_log2,
-                          m, l, o);
+                          softcap, m, l, o);
       __syncwarp();
       if (lane == 0) mbar_arrive(empty + s);
     }
@@ -781,7 +793,7 @@ attn_decode_shares_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv
                           const int* __restrict__ qo_indptr, const int* __restrict__ positions,
                           const int* __restrict__ kv_len,
                           const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int n_entries, int Hq,
-                          int Hkv, int page_size, float scale_log2, int window, int max_parts, int rows_pe,
+                          int Hkv, int page_size, float scale_log2, float softcap, int window, int max_parts, int rows_pe,
                           int row_tiles, int max_q_short,
                     const float* __restrict__ sink_l2) {
   // Lengths, positions and block tables were uploaded before the step's first kernel, and every cached key below
@@ -917,7 +929,7 @@ attn_decode_shares_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv
         const int key0 = pc.k_begin + k * KT;
         if (key0 + 16 * warp < pc.k_end)
           block16<HD, true>(qf, Ks, Ks + TILE_ELEMS, 16 * warp, key0, lim[0], lim[1], lo[0], lo[1], pc.k_end,
-                            scale_log2, m, l, o);
+                            scale_log2, softcap, m, l, o);
         __syncwarp();
         if (k + 1 < pc.n_tiles) {
           if (lane == 0) mbar_arrive(empty + s);
@@ -1047,7 +1059,7 @@ template <int HD> size_t decode_shares_smem() {
 template <int HD, bool TMA_TILE>
 __device__ __forceinline__ void block64(const uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* Ks,
                                         const __nv_bfloat16* Vs, int key0, int row_lim0, int row_lim1, int row_lo0,
-                                        int row_lo1, int k_end, bool need_mask, float scale_log2, float (&m)[2],
+                                        int row_lo1, int k_end, bool need_mask, float scale_log2, float softcap, float (&m)[2],
                                         float (&l)[2], float (&o)[HD / 8][4]) {
   const int lane = threadIdx.x & 31;
   const int mat = lane >> 3, r8 = lane & 7;
@@ -1075,7 +1087,7 @@ __device__ __forceinline__ void block64(const uint32_t (&qf)[HD / 16][4], const 
         const int key = key0 + 8 * nt + 2 * (lane & 3) + (i & 1);
         const int lim = (i >> 1) ? row_lim1 : row_lim0, lo = (i >> 1) ? row_lo1 : row_lo0;
         const bool ok = key <= lim && key >= lo && key < k_end;
-        s[nt][i] = ok ? s[nt][i] * scale_log2 : -INFINITY;
+        s[nt][i] = ok ? score2(s[nt][i], scale_log2, softcap) : -INFINITY;
         mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
       }
   } else {
@@ -1083,7 +1095,7 @@ __device__ __forceinline__ void block64(const uint32_t (&qf)[HD / 16][4], const 
     for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        s[nt][i] *= scale_log2;
+        s[nt][i] = score2(s[nt][i], scale_log2, softcap);
         mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
       }
   }
@@ -1138,7 +1150,7 @@ attn_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_b
                         long long q_row_stride, __nv_bfloat16* __restrict__ out, int* __restrict__ status,
                         const int* __restrict__ qo_indptr, const int* __restrict__ positions,
                         const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
-                        int page_size, float scale_log2, int window, int min_q_long,
+                        int page_size, float scale_log2, float softcap, int window, int min_q_long,
                     const float* __restrict__ sink_l2) {
   bspec::pdl_prologue(9);
   extern __shared__ unsigned char smem_dyn[];
@@ -1255,7 +1267,7 @@ attn_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_b
     const int key0 = k_begin + it * KT;
     if (warp_live && key0 <= warp_hi) {
       const bool need_mask = key0 + KT - 1 > warp_full || key0 < warp_lo || key0 + KT > k_end;
-      block64<HD, true>(qf, Ks, Ks + TILE_ELEMS, key0, lim[0], lim[1], lo[0], lo[1], k_end, need_mask, scale_log2, m,
+      block64<HD, true>(qf, Ks, Ks + TILE_ELEMS, key0, lim[0], lim[1], lo[0], lo[1], k_end, need_mask, scale_log2, softcap, m,
                         l, o);
     }
     __syncwarp();
@@ -1293,7 +1305,7 @@ __global__ void __launch_bounds__(NTHREADS)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, __nv_bfloat16* __restrict__ out,
                     const __nv_bfloat16* __restrict__ cache, const int* __restrict__ qo_indptr,
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
-                    const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
+                    const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, float softcap, int window,
                     int min_q_long, long long n_pages,
                     const float* __restrict__ sink_l2) {
   bspec::pdl_prologue(9);
@@ -1362,7 +1374,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
 #pragma unroll
       for (int kb = 0; kb < KT; kb += 16)
         if (key0 + kb <= warp_hi)
-          block16<HD>(qf, Ks, Vs, kb, key0, lim[0], lim[1], lo[0], lo[1], k_end, scale_log2, m, l, o);
+          block16<HD>(qf, Ks, Vs, kb, key0, lim[0], lim[1], lo[0], lo[1], k_end, scale_log2, softcap, m, l, o);
     }
     __syncthreads();
   }
@@ -1399,7 +1411,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
            const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens, int max_q_len, int Hq, int Hkv,
            int page_size, float scale, int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
            cudaStream_t stream, int balanced = 0, const int* kv_len = nullptr,
-           long long check_pages = 0x7fffffffffffll, const float* sink_l2 = nullptr) {
+           long long check_pages = 0x7fffffffffffll, const float* sink_l2 = nullptr, float softcap = 0.f) {
   const float scale_log2 = scale * 1.4426950408889634f;
   const int G = Hq / Hkv;
   // The opt-in to large shared memory and the resident-CTA count are facts of a device: set up once per device,
@@ -1436,7 +1448,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
         // equal shares of the tiles over as many CTAs as the device holds at once, then the join
         BSPEC_LAUNCH((attn_decode_shares_kernel<HD>), dim3(resident), DECODE_TMA_THREADS, decode_shares_smem<HD>(),
                      stream, kv_map, q, q_row_stride, out, o_part, ml_part, tile_counters, status, qo_indptr, positions,
-                     kv_len, kv_indptr, kv_indices, n_entries, Hq, Hkv, page_size, scale_log2, window, n_splits,
+                     kv_len, kv_indptr, kv_indices, n_entries, Hq, Hkv, page_size, scale_log2, softcap, window, n_splits,
                      short_q, row_tiles, max_q_short, sink_l2);
         launched = true;
        }
@@ -1444,14 +1456,14 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
       if (!launched && make_map_2d_bf16(&kv_map, cache, kv_rows, HD, page_size, 64)) {
         BSPEC_LAUNCH((attn_decode_tma_kernel<HD>), grid, DECODE_TMA_THREADS, decode_tma_smem<HD>(), stream, kv_map, q,
                      q_row_stride, out, o_part, ml_part, tile_counters, status, qo_indptr, positions, kv_indptr,
-                     kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short, sink_l2);
+                     kv_indices, Hq, Hkv, page_size, scale_log2, softcap, window, n_splits, row_tiles, max_q_short, sink_l2);
         launched = true;
       }
     }
     if (!launched)
       BSPEC_LAUNCH((attn_decode_kernel<HD>), grid, NTHREADS, decode_smem<HD>(), stream,
                    q, q_row_stride, out, o_part, ml_part, tile_counters, cache, qo_indptr, positions, kv_indptr,
-                   kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short, check_pages,
+                   kv_indices, Hq, Hkv, page_size, scale_log2, softcap, window, n_splits, row_tiles, max_q_short, check_pages,
                    sink_l2);
     const int err = (int)cudaGetLastError();
     if (err) return err;
@@ -1466,7 +1478,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
         dim3 grid((max_q_len * G + PREFILL_ROWS - 1) / PREFILL_ROWS, Hkv, n_entries);
         BSPEC_LAUNCH((attn_prefill_tma_kernel<HD>), grid, PREFILL_TMA_THREADS, prefill_tma_smem<HD>(), stream, kv_map,
                      q, q_row_stride, out, status, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
-                     scale_log2, window, max_q_short + 1, sink_l2);
+                     scale_log2, softcap, window, max_q_short + 1, sink_l2);
         launched = true;
       }
      }
@@ -1475,7 +1487,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
       dim3 grid((max_q_len * G + 63) / 64, Hkv, n_entries);
       BSPEC_LAUNCH((attn_prefill_kernel<HD>), grid, NTHREADS, prefill_smem<HD>(), stream,
                    q, q_row_stride, out, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
-                   scale_log2, window, max_q_short + 1, check_pages, sink_l2);
+                   scale_log2, softcap, window, max_q_short + 1, check_pages, sink_l2);
     }
     return (int)cudaGetLastError();
   }
@@ -1502,7 +1514,7 @@ BSPEC_API int bspec_attention_bf16_masked(const void* q, long long q_row_stride,
                                           const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens,
                                           int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale, int window,
                                           int n_splits, int max_q_short, int run_decode, int run_prefill, int balanced,
-                                          const int* kv_len, long long pages_in_all, const float* sink_l2,
+                                          const int* kv_len, long long pages_in_all, const float* sink_l2, float softcap,
                                           cudaStream_t stream);
 BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
                                    int* tile_counters, int* status, long long n_pages, const void* cache, const int* qo_indptr, const int* positions,
@@ -1513,19 +1525,19 @@ BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* 
   return bspec_attention_bf16_masked(q, q_row_stride, out, o_part, ml_part, tile_counters, status, n_pages, cache,
                                      qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, n_tokens,
                                      max_q_len, Hq, Hkv, hd, page_size, scale, window, n_splits, max_q_short, run_decode,
-                                     run_prefill, balanced, kv_len, pages_in_all, nullptr, stream);
+                                     run_prefill, balanced, kv_len, pages_in_all, nullptr, 0.f, stream);
 }
 
 // The same with the other masks and a sink.  ``window`` < 0: a chunk mask of -window positions (a query sees the
 // keys of its own chunk).  ``sink_l2`` (may be null): float32 per query head, the sink times log2(e); it joins the
-// softmax denominator as exp(sink).
+// softmax denominator as exp(sink).  ``softcap`` c > 0: a scaled score s becomes c tanh(s / c).
 BSPEC_API int bspec_attention_bf16_masked(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
                                           int* tile_counters, int* status, long long n_pages, const void* cache,
                                           const int* qo_indptr, const int* positions, const int* tok_entry,
                                           const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens,
                                           int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale, int window,
                                           int n_splits, int max_q_short, int run_decode, int run_prefill, int balanced,
-                                          const int* kv_len, long long pages_in_all, const float* sink_l2,
+                                          const int* kv_len, long long pages_in_all, const float* sink_l2, float softcap,
                                           cudaStream_t stream) {
   if (n_entries <= 0 || n_tokens <= 0) return 0;
   if (Hq % Hkv != 0 || n_splits < 1 || n_splits > 64) return (int)cudaErrorInvalidValue;
@@ -1533,7 +1545,7 @@ BSPEC_API int bspec_attention_bf16_masked(const void* q, long long q_row_stride,
   return launch<HDV>((const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, o_part, ml_part, tile_counters,   \
                      status, n_pages * 2 * Hkv * page_size, (const __nv_bfloat16*)cache, qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, \
                      n_tokens, max_q_len, Hq, Hkv, page_size, scale, window, n_splits, max_q_short, run_decode,      \
-                     run_prefill, stream, balanced, kv_len, pages_in_all > 0 ? pages_in_all : 0x7fffffffffffll, sink_l2)
+                     run_prefill, stream, balanced, kv_len, pages_in_all > 0 ? pages_in_all : 0x7fffffffffffll, sink_l2, softcap)
   if (hd == 64) GO(64);
   if (hd == 128) GO(128);
   if (hd == 256) GO(256);

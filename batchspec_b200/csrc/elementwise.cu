@@ -499,6 +499,35 @@ BSPEC_API int bspec_bigram_add(float* resid, const int* ids, const int* position
   return BSPEC_LAUNCH_CHECK();
 }
 
+// out[t, j] = x[t, j] * sigmoid(gate[t, j]) * factor (gate float32 or null: no gate); rows of x are dense, rows of gate
+// and out have strides of their own.
+template <typename T>
+__global__ void gate_mul_kernel(const T* __restrict__ x, const float* __restrict__ gate, long long gate_stride,
+                                T* __restrict__ out, long long out_stride, int width, float factor) {
+  bspec::pdl_prologue(68);
+  const size_t t = blockIdx.y;
+  for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < width; j += gridDim.x * blockDim.x) {
+    float v = to_f32(x[t * width + j]) * factor;
+    if (gate != nullptr) v = __fdividef(v, 1.f + __expf(-gate[t * gate_stride + j]));
+    out[t * out_stride + j] = from_f32<T>(v);
+  }
+}
+
+BSPEC_API int bspec_gate_mul(const void* x, const float* gate, long long gate_stride, void* out, long long out_stride,
+                             int dtype, int n, int width, float factor, cudaStream_t stream) {
+  if (n <= 0 || width <= 0) return 0;
+  if (n > 65535 * 32) return (int)cudaErrorInvalidConfiguration;
+  const dim3 grid((width + 255) / 256, n);
+  if (n > 65535) return (int)cudaErrorInvalidConfiguration;
+  if (dtype == BSPEC_F32)
+    BSPEC_LAUNCH((gate_mul_kernel<float>), grid, 256, 0, stream, (const float*)x, gate, gate_stride, (float*)out,
+                 out_stride, width, factor);
+  else
+    BSPEC_LAUNCH((gate_mul_kernel<__nv_bfloat16>), grid, 256, 0, stream, (const __nv_bfloat16*)x, gate, gate_stride,
+                 (__nv_bfloat16*)out, out_stride, width, factor);
+  return BSPEC_LAUNCH_CHECK();
+}
+
 // In place on float32: x *= factor.
 __global__ void scale_kernel(float* __restrict__ x, size_t total, float factor) {
   bspec::pdl_prologue(64);

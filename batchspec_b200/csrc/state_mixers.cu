@@ -23,21 +23,28 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 
 // ---------------------------------------------------------------- lightning attention
 // Block: COLS value columns of one head of one request, 8 lanes per column; lane r of a column keeps rows
-// r, r + 8, ... of that column of S in registers (NR of them).  Tokens are staged TT at a time in shared memory.
+// 32 g + 4 r + e (e < 4, g < NR / 4) of that column of S in registers, so that a lane reads its four rows of q and k
+// from shared memory in one 16-byte load.  Tokens are staged TT at a time in shared memory: the raw projection
+// columns of the next TT tokens are fetched into registers while the recurrence runs over the current ones, so the
+// memory latency is paid once per kernel and not once per batch of tokens.  The recurrence takes four tokens per
+// pass (sixteen independent chains of four dependent multiply-adds); a token's sums run in the same order in the
+// four-token pass and in the single-token tail, so a position's result does not depend on where a portion ends.
 // State of a request: [H][vdim][dim] float32 at state + slot * state_stride.
 constexpr int LT_COLS = 16;
 constexpr int LT_TT = 16;
-constexpr int LT_MAX_DIM = 256;
+constexpr int LT_THREADS = LT_COLS * 8;
 
 template <int NR>
-__global__ void __launch_bounds__(LT_COLS * 8)
+__global__ void __launch_bounds__(LT_THREADS)
 lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_off, int k_off, int v_off,
                             const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
                             const int* __restrict__ qo_indptr, const int* __restrict__ state_slots,
                             float* __restrict__ out, int H, int dim, int vdim) {
   bspec::pdl_prologue_late(65);
-  __shared__ float qs[LT_TT][LT_MAX_DIM];
-  __shared__ float ks[LT_TT][LT_MAX_DIM];
+  constexpr int DM = 8 * NR;                                // rows of S this instance holds (dim <= DM)
+  constexpr int VR = LT_TT * LT_COLS / LT_THREADS;          // staged v values per thread
+  __shared__ __align__(16) float qs[LT_TT][DM];
+  __shared__ __align__(16) float ks[LT_TT][DM];
   __shared__ float vs[LT_TT][LT_COLS];
   const int e = blockIdx.z, h = blockIdx.y;
   const int col = threadIdx.x >> 3, r = threadIdx.x & 7;
@@ -46,49 +53,106 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
   const int t0 = qo_indptr[e], nt = qo_indptr[e + 1] - t0;
   const float d = decay[h];
   float* sp = state + (size_t)state_slots[e] * state_stride + ((size_t)h * vdim + (live ? j : 0)) * dim;
+  float qn[NR], kn[NR], vn[VR];
+  // the raw columns of tokens base .. base + TT - 1 (zeros beyond the portion, the head's rows and the columns)
+  auto fetch = [&](int base) {
+    const int cnt = min(LT_TT, nt - base);
+#pragma unroll
+    for (int u = 0; u < NR; ++u) {
+      const int x = threadIdx.x + LT_THREADS * u;
+      const int tt = x / DM, i = x % DM;
+      const bool ok = tt < cnt && i < dim;
+      const float* row = proj + (size_t)(t0 + base + (ok ? tt : 0)) * ld + (size_t)h * dim + (ok ? i : 0);
+      qn[u] = ok ? row[q_off] : 0.f;
+      kn[u] = ok ? row[k_off] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < VR; ++u) {
+      const int x = threadIdx.x + LT_THREADS * u;
+      const int tt = x / LT_COLS, c = x % LT_COLS;
+      const int jj = blockIdx.x * LT_COLS + c;
+      const bool ok = tt < cnt && jj < vdim;
+      vn[u] = ok ? proj[(size_t)(t0 + base + tt) * ld + v_off + (size_t)h * vdim + jj] : 0.f;
+    }
+  };
+  if (nt > 0) fetch(0);
   float s[NR];
 #pragma unroll
   for (int m = 0; m < NR; ++m) {
-    const int i = r + 8 * m;
+    const int i = 32 * (m >> 2) + 4 * r + (m & 3);
     s[m] = (live && i < dim) ? sp[i] : 0.f;
   }
   for (int base = 0; base < nt; base += LT_TT) {
     const int cnt = min(LT_TT, nt - base);
     __syncthreads();
-    for (int x = threadIdx.x; x < cnt * dim; x += blockDim.x) {
-      const int tt = x / dim, i = x - tt * dim;
-      const float* row = proj + (size_t)(t0 + base + tt) * ld + (size_t)h * dim + i;
-      qs[tt][i] = silu_f(row[q_off]);
-      ks[tt][i] = silu_f(row[k_off]);
+#pragma unroll
+    for (int u = 0; u < NR; ++u) {
+      const int x = threadIdx.x + LT_THREADS * u;
+      qs[x / DM][x % DM] = silu_f(qn[u]);                    // silu(0) = 0: rows beyond dim and tokens beyond cnt
+      ks[x / DM][x % DM] = silu_f(kn[u]);
     }
-    for (int x = threadIdx.x; x < cnt * LT_COLS; x += blockDim.x) {
-      const int tt = x / LT_COLS, c = x - tt * LT_COLS;
-      const int jj = blockIdx.x * LT_COLS + c;
-      vs[tt][c] = jj < vdim ? silu_f(proj[(size_t)(t0 + base + tt) * ld + v_off + (size_t)h * vdim + jj]) : 0.f;
+#pragma unroll
+    for (int u = 0; u < VR; ++u) {
+      const int x = threadIdx.x + LT_THREADS * u;
+      vs[x / LT_COLS][x % LT_COLS] = silu_f(vn[u]);
     }
     __syncthreads();
-    for (int tt = 0; tt < cnt; ++tt) {
+    if (base + LT_TT < nt) fetch(base + LT_TT);
+    float* orow = out + (size_t)(t0 + base) * H * vdim + (size_t)h * vdim + j;
+    int tt = 0;
+    for (; tt + 4 <= cnt; tt += 4) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f}, vj[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) vj[a] = vs[tt + a][col];
+#pragma unroll
+      for (int g = 0; g < NR / 4; ++g) {
+        float4 k4[4], q4[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          k4[a] = *reinterpret_cast<const float4*>(&ks[tt + a][32 * g + 4 * r]);
+          q4[a] = *reinterpret_cast<const float4*>(&qs[tt + a][32 * g + 4 * r]);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const float kk[4] = {k4[a].x, k4[a].y, k4[a].z, k4[a].w}, qq[4] = {q4[a].x, q4[a].y, q4[a].z, q4[a].w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            s[4 * g + c] = __fmaf_rn(d, s[4 * g + c], __fmul_rn(kk[c], vj[a]));
+            acc[a] = __fmaf_rn(s[4 * g + c], qq[c], acc[a]);
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1)
+#pragma unroll
+        for (int a = 0; a < 4; ++a) acc[a] += __shfl_xor_sync(0xffffffffu, acc[a], o);
+      const float mine = r == 0 ? acc[0] : (r == 1 ? acc[1] : (r == 2 ? acc[2] : acc[3]));
+      if (live && r < 4) orow[(size_t)(tt + r) * H * vdim] = mine;
+    }
+    for (; tt < cnt; ++tt) {
       const float vj = vs[tt][col];
       float acc = 0.f;
 #pragma unroll
-      for (int m = 0; m < NR; ++m) {
-        const int i = r + 8 * m;
-        if (i < dim) {
-          s[m] = d * s[m] + ks[tt][i] * vj;
-          acc += s[m] * qs[tt][i];
+      for (int g = 0; g < NR / 4; ++g) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][32 * g + 4 * r]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][32 * g + 4 * r]);
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          s[4 * g + c] = __fmaf_rn(d, s[4 * g + c], __fmul_rn(kk[c], vj));
+          acc = __fmaf_rn(s[4 * g + c], qq[c], acc);
         }
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (live && r == 0) out[(size_t)(t0 + base + tt) * H * vdim + (size_t)h * vdim + j] = acc;
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (live && r == 0) orow[(size_t)tt * H * vdim] = acc;
     }
   }
   bspec::pdl_launch_dependents();
   if (live) {
 #pragma unroll
     for (int m = 0; m < NR; ++m) {
-      const int i = r + 8 * m;
+      const int i = 32 * (m >> 2) + 4 * r + (m & 3);
       if (i < dim) sp[i] = s[m];
     }
   }
@@ -210,11 +274,11 @@ BSPEC_API int bspec_lightning_recurrence(const float* proj, long long ld, int q_
                                          const int* qo_indptr, const int* state_slots, float* out, int n_entries, int H,
                                          int dim, int vdim, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
-  if (dim <= 0 || dim > LT_MAX_DIM || vdim <= 0 || H <= 0 || H > 65535 || n_entries > 65535)
+  if (dim <= 0 || dim > 256 || vdim <= 0 || H <= 0 || H > 65535 || n_entries > 65535)
     return (int)cudaErrorInvalidValue;
   const dim3 grid((vdim + LT_COLS - 1) / LT_COLS, H, n_entries);
 #define LL(NR)                                                                                                     \
-  BSPEC_LAUNCH_SERIALIZED((lightning_recurrence_kernel<NR>), grid, LT_COLS * 8, 0, stream, proj, ld, q_off, k_off, \
+  BSPEC_LAUNCH_SERIALIZED((lightning_recurrence_kernel<NR>), grid, LT_THREADS, 0, stream, proj, ld, q_off, k_off, \
                           v_off, decay, state, state_stride, qo_indptr, state_slots, out, H, dim, vdim)
   if (dim <= 32) LL(4); else if (dim <= 64) LL(8); else if (dim <= 128) LL(16); else LL(32);
 #undef LL

@@ -49,6 +49,7 @@ _SIGNATURES = {
     "bspec_bigram_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_scale": [c_void_p, c_longlong, c_float, c_void_p],
+    "bspec_gate_mul": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_float, c_void_p],
     "bspec_lightning_recurrence": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p,
                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_scan_conv": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
@@ -116,7 +117,7 @@ _SIGNATURES = {
     "bspec_attention_bf16_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                    c_longlong, c_void_p, c_void_p],
+                                    c_longlong, c_void_p, c_float, c_void_p],
     "bspec_attention_prefill_tc_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int,
                                           c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -634,9 +635,22 @@ def sink_table(sink: torch.Tensor) -> torch.Tensor:
     return (sink.to(torch.float32) * 1.4426950408889634).contiguous()
 
 
+def gate_mul(x: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, factor: float = 1.0) -> None:
+    """out = x * sigmoid(gate) * factor.  ``x`` [n, w] contiguous; ``gate`` a float32 view [n, w] of rows that may be
+    wider, or None for no gate; ``out`` a view [n, w] of rows that may be wider."""
+    _require_cuda(x, gate, out)
+    n, w = x.shape
+    assert x.is_contiguous() and out.shape == x.shape and out.stride(1) == 1 and out.dtype == x.dtype
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape == x.shape and gate.stride(1) == 1)
+    _check(load_library().bspec_gate_mul(x.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                         out.data_ptr(), out.stride(0), _dtype_code(x.dtype), n, w, float(factor),
+                                         _stream()), "gate_mul")
+
+
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables, n_heads: int,
                     n_kv_heads: int, head_dim: int, scale: float, window: int = 0, chunk: int = 0,
-                    sink: Optional[torch.Tensor] = None, sink_l2: Optional[torch.Tensor] = None) -> None:
+                    sink: Optional[torch.Tensor] = None, sink_l2: Optional[torch.Tensor] = None,
+                    softcap: float = 0.0) -> None:
     """Causal attention of the step's tokens over their requests' cached keys.
     ``qkv``: [n, >= n_heads*head_dim] rows with the (already rotated) query heads
     first.  ``ctx`` gives qo_indptr / positions / n_entries / max_q_len, ``tables``
@@ -644,7 +658,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
     on the tensor-core kernels; everything else on the generic float32-math kernel.
     ``window`` > 0 keeps the last ``window`` keys, ``chunk`` > 0 the keys of the query's own chunk of ``chunk``
     positions (one of the two at most).  ``sink`` (float32 per query head, with ``sink_l2`` its ``sink_table``) adds
-    exp(sink) to the softmax denominator."""
+    exp(sink) to the softmax denominator.  ``softcap`` c > 0 turns a scaled score s into c tanh(s / c) (the tcgen05
+    prompt kernel knows no cap; capped layers run on the other tensor-core kernels)."""
     _require_cuda(qkv, out, cache, sink, sink_l2)
     assert qkv.stride(1) == 1 and out.is_contiguous() and out.dtype == qkv.dtype == cache.dtype
     assert not (window and chunk) and window >= 0 and chunk >= 0
@@ -661,7 +676,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
             plan = ctx.extras[key] = _attention_plan(qkv.device, ctx, tables, n_heads, n_kv_heads, head_dim)
         (tma, balanced, n_splits, short, run_decode, run_prefill, prefill_tc, o_part, ml_part, counters, status, qo, pos,
          tok_entry, kv_indptr, kv_indices, kv_len) = plan
-        if prefill_tc:
+        if prefill_tc and not softcap:
             # long portions on the tcgen05 kernel; what is left for the call below are the short requests
             _check(lib.bspec_attention_prefill_tc_masked(
                 qkv.data_ptr(), qkv.stride(0), out.data_ptr(), status, cache.shape[0], cache.data_ptr(), qo, pos,
@@ -676,7 +691,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), o_part, ml_part, counters, status,
             cache.shape[0] if tma else 0, cache.data_ptr(), qo, pos, tok_entry, kv_indptr, kv_indices, ctx.n_entries,
             ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size, float(scale), mask,
-            n_splits, short, run_decode, run_prefill, balanced, kv_len, cache.shape[0], _ptr(sink_l2), _stream()),
+            n_splits, short, run_decode, run_prefill, balanced, kv_len, cache.shape[0], _ptr(sink_l2), float(softcap),
+            _stream()),
             "attention_bf16")
         global _launches
         _launches += 1 if run_decode and run_prefill else 0
@@ -685,7 +701,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(qkv.dtype),
         ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
         ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, head_dim, tables.page_size, float(scale),
-        int(window), int(chunk), _ptr(sink), cache.shape[0], 0.0, 0, None, 0, out.stride(0), 1.0, _stream()),
+        int(window), int(chunk), _ptr(sink), cache.shape[0], float(softcap), 0, None, 0, out.stride(0), 1.0, _stream()),
         "attention_generic")
 
 

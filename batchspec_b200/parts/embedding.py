@@ -18,8 +18,9 @@ class BigramHash(InputPart):
     graph_safe = True
 
     def __init__(self, runtime: Runtime, dim: int, vocab: int, buckets: int, mul_prev: int, mul_cur: int):
-        if buckets <= 0:
-            raise ValueError(f"a hashed table needs at least one bucket, got {buckets}")
+        if buckets <= 0 or not (0 <= mul_prev < 2 ** 31 and 0 <= mul_cur < 2 ** 31):
+            raise ValueError(f"a hashed table needs at least one bucket and multipliers in [0, 2^31), got {buckets}, "
+                             f"{mul_prev}, {mul_cur}")
         self.runtime, self.dim, self.vocab = runtime, int(dim), int(vocab)
         self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
         self.table = None

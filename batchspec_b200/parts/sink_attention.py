@@ -61,6 +61,10 @@ class SinkAttention(Mixer):
             raise ValueError("give a chunk size or a window, both positive, not both")
         self.position = build_part(POSITION_ENCODINGS, position, runtime)
         self.wqkv = self.wo = self.b = self.sinks = self.sinks_l2 = None
+        # values that are the keys, at sizes the tensor-core kernels take: those kernels read keys and values from
+        # places of their own, so the key rows of the fused product are listed twice and every key is stored as its
+        # own value too (twice the pages, tensor-core speed); at other sizes the pages hold keys only
+        self.copy_keys = self.values_are_keys and self._tensor_cores(runtime.dtype)
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         q, k, v = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim, self.n_kv_heads * self.v_dim
@@ -79,6 +83,8 @@ class SinkAttention(Mixer):
 
     def bind(self, params):
         names = ("q", "k") if self.values_are_keys else ("q", "k", "v")
+        if self.copy_keys:
+            names = ("q", "k", "k")
         self.qkv_width = sum(params[n].shape[0] for n in names)
         # the gate's rows ride in the same product, after q, k and v
         self.wqkv = torch.cat([params[n] for n in names + (("g",) if self.gate else ())], dim=0).contiguous()
@@ -92,6 +98,9 @@ class SinkAttention(Mixer):
             self.sinks = torch.full((self.n_heads,), self.fixed_sink, dtype=torch.float32, device=self.wo.device)
             self.sinks_l2 = ops.sink_table(self.sinks)
 
+    def _tensor_cores(self, dtype) -> bool:
+        return dtype == torch.bfloat16 and self.v_dim == self.head_dim and self.head_dim in (64, 128, 256)
+
     @property
     def out_width(self) -> int:
         """Width of what ``pre_projection`` returns (the output projection's input)."""
@@ -100,7 +109,7 @@ class SinkAttention(Mixer):
     def cache_spec(self) -> CacheSpec:
         policy = "chunk" if self.chunk else ("window" if self.window else "full")
         span = self.chunk or self.window or None
-        if self.values_are_keys:
+        if self.values_are_keys and not self.copy_keys:
             return CacheSpec(policy, (self.n_kv_heads * self.head_dim,), span, tensors=1)
         if self.v_dim == self.head_dim:
             return CacheSpec(policy, (self.n_kv_heads, self.head_dim), span)
@@ -123,20 +132,25 @@ class SinkAttention(Mixer):
         qkv = proj[:, :self.qkv_width]
         gate = proj[:, self.qkv_width:] if self.gate else None
         with bucket("attn.rope"):
-            q = ops.qkv_prepare(qkv, H, G, hd, 0 if self.values_are_keys else vd, self.b, getattr(pos, "inv_freq", None),
+            q = ops.qkv_prepare(qkv, H, G, hd, 0 if self.values_are_keys and not self.copy_keys else vd, self.b, getattr(pos, "inv_freq", None),
                                 getattr(pos, "rotary_dim", 0), getattr(pos, "interleaved", False),
                                 getattr(pos, "magnitude", 1.0), self.qk_norm_eps, ctx.positions, ctx.tok_entry,
                                 tables.kv_indptr, tables.kv_indices, cache.kv, tables.page_size, write_kv=cache.owner)
         if out is None:
             out = torch.empty((n, H * vd), dtype=x.dtype, device=x.device)
-        plain = not (self.softcap or self.values_are_keys or self.gate) and out_scale == 1.0 and out.is_contiguous()
         with bucket("attn.compute"):
-            if vd == hd and plain:
-                # values as wide as keys: the plain attention part's kernels (tensor cores for bfloat16 heads of
-                # 64, 128 or 256), which take the chunk mask and the sink too
-                ops.paged_attention(q, out, cache.kv, ctx, tables, H, G, hd, self.scale, self.window, self.chunk,
-                                    self.sinks, self.sinks_l2)
+            if self._tensor_cores(x.dtype):
+                # bfloat16 heads of 64, 128 or 256 with values as wide as keys: the plain attention part's tensor-core
+                # kernels, which take the masks, the sink and the soft cap; gate and factor follow in a kernel of
+                # their own
+                direct = not self.gate and out_scale == 1.0 and out.is_contiguous()
+                heads = out if direct else torch.empty((n, H * vd), dtype=x.dtype, device=x.device)
+                ops.paged_attention(q, heads, cache.kv, ctx, tables, H, G, hd, self.scale, self.window, self.chunk,
+                                    self.sinks, self.sinks_l2, self.softcap)
+                if not direct:
+                    ops.gate_mul(heads, gate, out, out_scale)
             else:
                 ops.masked_attention(q, out, cache.kv, ctx, tables, H, G, hd, vd, self.scale, self.window, self.chunk,
-                                     self.sinks, self.softcap, self.values_are_keys, gate, out_scale)
+                                     self.sinks, self.softcap, self.values_are_keys and not self.copy_keys, gate,
+                                     out_scale)
         return out

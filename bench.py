@@ -520,7 +520,144 @@ def lupusun_kernels_alone(z, pk, iters=20):
     return out
 
 
+TOKOLORN_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, chunk=1024, window=1024, inner=4096, state=16, dt_rank=128,
+                  delta_heads=16, delta_kv_heads=8, dense_ff=8448),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, chunk=1024, window=1024, inner=8192, state=16, dt_rank=256,
+                  delta_heads=32, delta_kv_heads=16, dense_ff=14336),
+}
+
+
+def tokolorn_config_json(z, layers, vocab=32000):
+    """Chunk attention, lightning attention, window attention beside a selective scan, lightning attention, and so
+    on in turn, each with a feed-forward; no loop, so that the depth equals the other models'."""
+    H, hd = z["heads"], z["dim"]
+    mlp = dict(kind="dense", ff=z["dense_ff"])
+    att = dict(type="attention", mlp=mlp, mixer=dict(heads=H, kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5,
+                                                     mask=dict(size=z["chunk"])))
+    lit = dict(type="lightning", mlp=mlp,
+               mixer=dict(heads=H, dim=hd, vdim=hd, decay=[1.0 - 2.0 ** (-(2.0 + 6.0 * i / (H - 1))) for i in range(H)]))
+    par = dict(type="parallel", mlp=mlp, mixer=dict(
+        left=dict(heads=H, kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5, softcap=30.0,
+                  mask=dict(size=z["window"]), rot=dict(base=500000.0, dims=hd)),
+        right=dict(inner=z["inner"], state=z["state"], dt_rank=z["dt_rank"], conv=4), left_scale=0.5, right_scale=0.5))
+    return dict(architecture="Tokolorn", vocab=vocab, width=z["width"], norm=dict(eps=1e-5), logit_scale=1.0,
+                embedding=dict(scale=1.0, bigram=dict(buckets=65521, mul_prev=31, mul_cur=7)),
+                layers=[(att, lit, par, lit)[i % 4] for i in range(layers)])
+
+
+def tokolorn_kernels_alone(z, pk, iters=20):
+    """The design's own kernels by themselves.  Attention (a prompt of 4,096 tokens: FLOP/s over the visible pairs
+    against the measured product peak; a decode step of 64 requests x 4,096 keys: bytes of visible keys and values
+    against the measured copy rate) with a window and a soft cap, and with a chunk mask and a sink, beside plain
+    causal attention; the lightning recurrence and the selective scan (decode: bytes of state read and written against
+    the copy rate; prompts: time per token), their neighbours (output norm, convolution, gate), and the bigram rows."""
+    import torch
+    from types import SimpleNamespace
+    from itertools import accumulate
+    from batchspec_b200.kernels import ops
+    ops.require("state_mixers")
+    dev = "cuda:0"
+    Hq, G, hd, ps = z["heads"], z["kv_heads"], z["dim"], 16
+    out = {}
+    sink = torch.zeros(Hq, device=dev)
+    sink_l2 = ops.sink_table(sink)
+
+    def step_ctx(q_lens, ctx_len):
+        n, B = sum(q_lens), len(q_lens)
+        pages_per = -(-ctx_len // ps)
+        qo = torch.tensor([0] + list(accumulate(q_lens)), dtype=torch.int32, device=dev)
+        pos = torch.cat([torch.arange(ctx_len - q, ctx_len) for q in q_lens]).to(dev, torch.int32)
+        ent = torch.cat([torch.full((q,), i) for i, q in enumerate(q_lens)]).to(dev, torch.int32)
+        ctx = SimpleNamespace(qo_indptr=qo, positions=pos, tok_entry=ent, n_entries=B, n_tokens=n, max_q_len=max(q_lens),
+                              max_kv_len=ctx_len, kv_len=torch.full((B,), ctx_len, dtype=torch.int32, device=dev),
+                              state_slots=torch.arange(B, dtype=torch.int32, device=dev),
+                              token_ids=torch.randint(0, 32000, (n,), dtype=torch.int32, device=dev),
+                              extras={"min_q_len": min(q_lens)})
+        tables = SimpleNamespace(kv_indptr=torch.arange(B + 1, dtype=torch.int32, device=dev) * pages_per,
+                                 kv_indices=torch.randperm(B * pages_per, device=dev).to(torch.int32), page_size=ps)
+        return ctx, tables, n, B, pages_per
+
+    for name, q_lens, ctx_len in (("prompt_4096", [4096], 4096), ("decode_64x4096", [1] * 64, 4096)):
+        ctx, tables, n, B, pages_per = step_ctx(q_lens, ctx_len)
+        cache = torch.randn(B * pages_per, 2, ps * G * hd, device=dev).bfloat16()
+        q = torch.randn(n, Hq * hd, device=dev).bfloat16()
+        o = torch.empty(n, Hq * hd, device=dev, dtype=torch.bfloat16)
+        for label, win, ck, sk, sk2, cap in (("window_cap", z["window"], 0, None, None, 30.0),
+                                             ("window", z["window"], 0, None, None, 0.0),
+                                             ("chunk_sink", 0, z["chunk"], sink, sink_l2, 0.0), ("causal", 0, 0, None, None, 0.0)):
+            ctx.extras = {"min_q_len": min(q_lens)}
+            ms = _time(lambda: ops.paged_attention(q, o, cache, ctx, tables, Hq, G, hd, hd ** -0.5, win, ck, sk, sk2, cap), iters)
+            first = lambda p: max(0, p - win + 1) if win else ((p // ck) * ck if ck else 0)
+            pairs = sum(p - first(p) + 1 for p in range(ctx_len - q_lens[0], ctx_len)) * len(q_lens)
+            if name.startswith("prompt"):
+                flops = 4.0 * Hq * hd * pairs
+                out[f"attention_{name}_{label}"] = dict(ms=round(ms, 4), tflops=round(flops / ms / 1e9, 1),
+                                                        frac_of_measured=round(flops / ms / 1e9 / pk["bf16_tflops"], 4))
+            else:
+                nbytes = pairs * 2 * G * hd * 2
+                out[f"attention_{name}_{label}"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+                                                        frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    # gate and factor after the attention, bigram rows after the embedding: bytes read and written
+    n = 4096
+    ctx, tables, _, _, _ = step_ctx([n], n)
+    heads = torch.randn(n, Hq * hd, device=dev).bfloat16()
+    gate = torch.randn(n, Hq * hd, device=dev)
+    both = torch.empty(n, Hq * hd + z["inner"], device=dev, dtype=torch.bfloat16)
+    ms = _time(lambda: ops.gate_mul(heads, gate, both[:, :Hq * hd], 0.5), iters)
+    nbytes = n * Hq * hd * (2 + 4 + 2)
+    out["gate_mul_4096"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    resid = torch.zeros(n, z["width"], device=dev)
+    table = torch.randn(65522, z["width"], device=dev).bfloat16()
+    prev = torch.zeros(4, 1, dtype=torch.int32, device=dev)
+    ms = _time(lambda: ops.bigram_add(resid, table, prev, ctx, 65521, 31, 7, 32000), iters)
+    nbytes = n * z["width"] * (4 + 4 + 2)
+    out["bigram_add_4096"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    # the two recurrences
+    H, dk, dv = z["heads"], hd, hd
+    inner, N, taps = z["inner"], z["state"], 4
+    decay = torch.linspace(0.75, 0.999, H, device=dev)
+    norm_w = torch.ones(H * dv, device=dev)
+    conv, conv_b = torch.randn(inner, taps, device=dev) * 0.5, torch.zeros(inner, device=dev)
+    a_log, d_skip, dt_b = torch.zeros(inner, N, device=dev), torch.ones(inner, device=dev), torch.zeros(inner, device=dev)
+    for name, q_lens in (("prompt_2048", [2048]), ("prompt_8x2048", [2048] * 8), ("decode_64", [1] * 64), ("decode_256", [1] * 256)):
+        ctx, tables, n, B, _ = step_ctx(q_lens, q_lens[0])
+        ld = 2 * H * dk + 2 * H * dv
+        proj = torch.randn(n, ld, device=dev)
+        state = torch.zeros(B, H * dv * dk, device=dev)
+        ms_r = _time(lambda: ops.lightning_recurrence(proj, 0, H * dk, 2 * H * dk, decay, state, ctx, H, dk, dv), iters)
+        o32 = ops.lightning_recurrence(proj, 0, H * dk, 2 * H * dk, decay, state, ctx, H, dk, dv)
+        ms_n = _time(lambda: ops.gated_rmsnorm(o32, proj[:, 2 * H * dk + H * dv:], norm_w, 1e-5, 1, H * dv, torch.bfloat16, "sigmoid"), iters)
+        rec = dict(recurrence_ms=round(ms_r, 4), out_norm_ms=round(ms_n, 4),
+                   out_norm_frac_of_measured=round(n * H * dv * (4 + 4 + 2) / ms_n / 1e6 / pk["hbm_gbs"], 4))
+        if name.startswith("decode"):
+            nbytes = B * H * dk * dv * 4 * 2                              # every state read and written once
+            rec["recurrence_gbs"] = round(nbytes / ms_r / 1e6, 1)
+            rec["recurrence_frac_of_measured"] = round(nbytes / ms_r / 1e6 / pk["hbm_gbs"], 4)
+        else:
+            rec["recurrence_ns_per_token"] = round(ms_r * 1e6 / q_lens[0], 1)
+            rec["recurrence_fp32_tflops"] = round(5.0 * n * H * dk * dv / ms_r / 1e9, 2)     # decay, k v^T, S^T q
+        out[f"lightning_{name}"] = rec
+        xz = torch.randn(n, 2 * inner, device=dev)
+        sstate = torch.zeros(B, N * inner + (taps - 1) * inner, device=dev)
+        ms_c = _time(lambda: ops.scan_conv(xz, conv, conv_b, sstate, N * inner, ctx, inner, taps, torch.bfloat16), iters)
+        xc, _ = ops.scan_conv(xz, conv, conv_b, sstate, N * inner, ctx, inner, taps, torch.bfloat16)
+        dt_raw, bc = torch.randn(n, inner, device=dev), torch.randn(n, 2 * N, device=dev)
+        y = torch.empty(n, inner, device=dev, dtype=torch.bfloat16)
+        ms_s = _time(lambda: ops.selective_scan(xz, xc, dt_raw, bc, a_log, d_skip, dt_b, sstate, N * inner, ctx, y, 0.5, inner, N, taps), iters)
+        rec = dict(conv_ms=round(ms_c, 4), scan_ms=round(ms_s, 4),
+                   conv_frac_of_measured=round(n * inner * (4 + 4 + 2) / ms_c / 1e6 / pk["hbm_gbs"], 4))
+        nbytes = B * inner * N * 4 * 2 + n * inner * (4 * 4 + 2)          # state once; x, z, xc, dt read, y written
+        rec["scan_gbs"] = round(nbytes / ms_s / 1e6, 1)
+        rec["scan_frac_of_measured"] = round(nbytes / ms_s / 1e6 / pk["hbm_gbs"], 4)
+        if not name.startswith("decode"):
+            rec["scan_ns_per_token"] = round(ms_s * 1e6 / q_lens[0], 1)
+        out[f"scan_{name}"] = rec
+    return out
+
+
 DESIGNS = {
+    "tokolorn": (TOKOLORN_SIZES, tokolorn_config_json, tokolorn_kernels_alone, "kernels_alone"),
     "vabanex": (VABANEX_SIZES, vabanex_config_json, latent_attention_alone, "latent_attention_alone"),
     "lupusun": (LUPUSUN_SIZES, lupusun_config_json, lupusun_kernels_alone, "kernels_alone"),
 }
@@ -540,7 +677,10 @@ def run_design(a) -> int:
     sizes, config_json, alone, alone_key = DESIGNS[a.design]
     for size, z in sizes.items():
         rec = {}
-        for label, cj in ((a.design, config_json(z, layers)), ("llama", llama_config_json(z, layers))):
+        models = [(a.design, config_json(z, layers)), ("llama", llama_config_json(z, layers))]
+        if a.design == "tokolorn":        # its closest model, the other one with recurrent state beside attention
+            models.append(("lupusun", lupusun_config_json(z, layers)))
+        for label, cj in models:
             cfg = config_from_json_dict(cj)
             eng = Engine(dtype="bfloat16", device="cuda:0")
             eng.load_model(config=cfg, random_seed=0, draw_on_device=True)
@@ -621,7 +761,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no prefill, b1, b64, e2e)")
     ap.add_argument("--skip-workloads", action="store_true",
                     help="leave out e2e at batch 64 and the 3B / long-context workloads (about a minute)")
-    ap.add_argument("--design", default=None, choices=["vabanex", "lupusun"],
+    ap.add_argument("--design", default=None, choices=["vabanex", "lupusun", "tokolorn"],
                     help="instead of the headline workload: this design at real layer sizes beside the Llama model of equal size")
     a = ap.parse_args()
     if a.impl == "reference":

@@ -213,7 +213,7 @@ def run_trace_subprocess(folder, dtype, steps, out_dir, max_tokens, extra_args=(
     return out
 
 
-def compare_with_oracle(got, folder, requests, dtype_name, expect=None, oracle=None, allow_over=0.0):
+def compare_with_oracle(got, folder, requests, dtype_name, expect=None, oracle=None, allow_over=0.0, allow_rows=0):
     """Every row against the plain implementation.  ``got`` has to hold exactly the rows ``expect`` (a set of
     (request, position); default: every position of every request), so a row that never came back fails the
     comparison instead of being skipped.  Returns the worst error and where it was."""
@@ -236,6 +236,6 @@ def compare_with_oracle(got, folder, requests, dtype_name, expect=None, oracle=N
                 worst = (err, (rid, p))
     # ``allow_over``: the share of rows that may be beyond the tolerance (a model with a router, in bfloat16: a
     # choice between two experts whose scores differ by less than the rounding falls either way)
-    assert over <= allow_over * rows, (f"{over} of {rows} rows beyond the tolerance, worst relative error "
+    assert over <= max(allow_over * rows, allow_rows), (f"{over} of {rows} rows beyond the tolerance, worst relative error "
                                        f"{worst[0]:.3e} at (request, position) {worst[1]}")
     return worst

@@ -43,19 +43,26 @@ def embed_rows(tokens: Sequence[int], table, bigram, scale: float, buckets: int,
     return torch.stack(rows)
 
 
+def decaying_linear_attention(q, k, v, decay: Sequence[float]):
+    """q, k [T, H, D], v [T, H, V]: per head S_t = decay_h S_(t-1) + k_t v_t^T (S_0 = 0), o_t = S_t^T q_t."""
+    T, heads, dim = q.shape
+    out = torch.zeros(T, heads, v.shape[2], dtype=F)
+    for j in range(heads):
+        S = torch.zeros(dim, v.shape[2], dtype=F)
+        for t in range(T):
+            S = decay[j] * S + torch.outer(k[t, j], v[t, j])
+            out[t, j] = S.T @ q[t, j]
+    return out
+
+
 def lightning(h, w: Dict[str, torch.Tensor], decay: Sequence[float], heads: int, dim: int, vdim: int, eps: float):
-    """Linear attention with a fixed decay per head: S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t; then the RMS
-    norm over all heads together (a weight per coordinate), the sigmoid gate and the output projection."""
+    """Linear attention with a fixed decay per head on silu(q), silu(k), silu(v); then the RMS norm over all heads
+    together (a weight per coordinate), the sigmoid gate and the output projection."""
     T = h.shape[0]
     q = silu(h @ f64(w["q"]).T).view(T, heads, dim)
     k = silu(h @ f64(w["k"]).T).view(T, heads, dim)
     v = silu(h @ f64(w["v"]).T).view(T, heads, vdim)
-    out = torch.zeros(T, heads, vdim, dtype=F)
-    for j in range(heads):
-        S = torch.zeros(dim, vdim, dtype=F)
-        for t in range(T):
-            S = decay[j] * S + torch.outer(k[t, j], v[t, j])
-            out[t, j] = S.T @ q[t, j]
+    out = decaying_linear_attention(q, k, v, decay)
     o = rms(out.reshape(T, heads * vdim), eps) * f64(w["norm"])
     o = o * torch.sigmoid(h @ f64(w["g"]).T)
     return o @ f64(w["o"]).T
@@ -110,32 +117,47 @@ def window_attention(h, w, m: dict):
     return o @ f64(w["o"]).T
 
 
-def selective_scan(h, w, m: dict):
-    """Mamba: in-projection [x | z], causal convolution and silu on x, input-dependent step dt, B and C, a diagonal
-    state per channel, a skip D x, the gate silu(z) and the output projection."""
-    T = h.shape[0]
-    inner, N, R, taps = m["inner"], m["state"], m["dt_rank"], m["conv"]
-    xz = h @ f64(w["in"]).T
-    x, z = xz[:, :inner], xz[:, inner:]
-    conv, cb = f64(w["conv"]), f64(w["conv.b"])
-    xc = torch.zeros_like(x)
+def causal_conv(x, conv, bias):
+    """x [T, C], conv [C, taps], bias [C]: y_t = bias + sum_j conv[:, j] x_(t - (taps-1) + j), zeros before the start
+    (the last column multiplies the token's own input)."""
+    T, taps = x.shape[0], conv.shape[1]
+    y = torch.zeros_like(x)
     for t in range(T):
-        acc = cb.clone()
+        acc = bias.clone()
         for j in range(taps):
             src = t - (taps - 1) + j
             if src >= 0:
                 acc = acc + conv[:, j] * x[src]
-        xc[t] = acc
-    xc = silu(xc)
-    p = xc @ f64(w["x"]).T
-    dt, B, C = p[:, :R], p[:, R:R + N], p[:, R + N:R + 2 * N]
-    dt = torch.nn.functional.softplus(dt @ f64(w["dt"]).T + f64(w["dt.b"]), threshold=1e9)
-    A = -torch.exp(f64(w["A_log"]))
-    S = torch.zeros(inner, N, dtype=F)
+        y[t] = acc
+    return y
+
+
+def softplus(x):
+    return torch.where(x > 40, x, torch.log1p(torch.exp(torch.clamp(x, max=40))))
+
+
+def diagonal_scan(x, dt, A, B, C, D):
+    """x, dt [T, I], A [I, N], B, C [T, N], D [I]: S <- exp(dt A) S + dt x B^T per channel, y = S C + D x."""
+    T, inner = x.shape
+    S = torch.zeros(inner, A.shape[1], dtype=F)
     y = torch.zeros(T, inner, dtype=F)
     for t in range(T):
-        S = torch.exp(dt[t][:, None] * A) * S + (dt[t] * xc[t])[:, None] * B[t][None, :]
-        y[t] = (S * C[t][None, :]).sum(1) + f64(w["D"]) * xc[t]
+        S = torch.exp(dt[t][:, None] * A) * S + (dt[t] * x[t])[:, None] * B[t][None, :]
+        y[t] = (S * C[t][None, :]).sum(1) + D * x[t]
+    return y
+
+
+def selective_scan(h, w, m: dict):
+    """Mamba: in-projection [x | z], causal convolution and silu on x, input-dependent step dt, B and C, a diagonal
+    state per channel, a skip D x, the gate silu(z) and the output projection."""
+    inner, N, R = m["inner"], m["state"], m["dt_rank"]
+    xz = h @ f64(w["in"]).T
+    x, z = xz[:, :inner], xz[:, inner:]
+    xc = silu(causal_conv(x, f64(w["conv"]), f64(w["conv.b"])))
+    p = xc @ f64(w["x"]).T
+    dt, B, C = p[:, :R], p[:, R:R + N], p[:, R + N:R + 2 * N]
+    dt = softplus(dt @ f64(w["dt"]).T + f64(w["dt.b"]))
+    y = diagonal_scan(xc, dt, -torch.exp(f64(w["A_log"])), B, C, f64(w["D"]))
     return (y * silu(z)) @ f64(w["o"]).T
 
 
@@ -206,3 +228,33 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: Sequence[int], 
     z = scalar_norm(x, tensors["final.norm"], cfg["norm"]["eps"])
     logits = (z @ f64(tensors["head"]).T) * cfg.get("logit_scale", 1.0)
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+# ---------------------------------------------------------------------------------------------- a model folder
+def read_tensors(path) -> Dict[str, torch.Tensor]:
+    """A safetensors file: an 8-byte little-endian length, that many bytes of JSON (name -> dtype, shape, offsets), the
+    data.  bfloat16 comes back as float32 with the same values."""
+    import json
+    import struct
+    import numpy as np
+    raw = open(path, "rb").read()
+    (n,) = struct.unpack("<Q", raw[:8])
+    data = raw[8 + n:]
+    out = {}
+    for name, meta in json.loads(raw[8:8 + n]).items():
+        if name == "__metadata__":
+            continue
+        lo, hi = meta["data_offsets"]
+        if meta["dtype"] == "BF16":
+            arr = (np.frombuffer(data[lo:hi], dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+        else:
+            arr = np.frombuffer(data[lo:hi], dtype={"F32": np.float32, "I32": np.int32, "F64": np.float64}[meta["dtype"]]).copy()
+        out[name] = torch.from_numpy(arr.copy()).reshape(meta["shape"])
+    return out
+
+
+def read_model_folder(folder):
+    import json
+    from pathlib import Path
+    folder = Path(folder)
+    return json.loads((folder / "config.json").read_text()), read_tensors(folder / "model.safetensors")
