@@ -220,7 +220,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
                        int* __restrict__ status, const int* __restrict__ qo_indptr, const int* __restrict__ positions,
                        const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
                        int n_entries, int n_items, int page_size, float scale_log2, int window, int min_q_long,
-                       int q_by_tma, int* __restrict__ work, const float* __restrict__ sink_l2) {
+                       int q_by_tma, int* __restrict__ work, const float* __restrict__ sink_l2, float cap_raw,
+                       float cap_x2) {
   // The step's lengths, positions and block tables were uploaded before its first kernel: the set-up below and the
   // look-up of the CTA's first item read nothing that the kernel before this one writes, so they run under its
   // tail; q, the new tokens' keys and `out` are touched only after the wait.
@@ -508,6 +509,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
         tc_ld32(s_addr, sv[0]);
         tc_ld32(s_addr + 32u, sv[1]);
         tc_wait_ld();
+        if (cap_raw > 0.f) {
+          // soft cap c on the scaled score: c tanh(scale s / c), kept in raw units (divided by the scale again) so
+          // that everything below stays as it is.  tanh(x) = 1 - 2 / (1 + e^(2x)); e^(2x) = inf gives 1, 0 gives -1
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float e2x = ex2(__uint_as_float(sv[c][i]) * cap_x2);
+              sv[c][i] = __float_as_uint(cap_raw * (1.f - __fdividef(2.f, 1.f + e2x)));
+            }
+        }
         // P = 2^(scale * S - m) for the row, its sum returned; scaling and the row sum handle two values per
         // instruction (fma/add.f32x2), the exponentials all go to the special-function unit (masked scores are -inf
         // and come out as exactly 0).  Each half of P goes back into tensor memory as soon as it is complete, over
@@ -697,6 +709,12 @@ BSPEC_API int bspec_attention_prefill_tc_masked(const void* q, long long q_row_s
                                                 int n_entries, long long n_tokens, int max_q_len, int Hq, int Hkv,
                                                 int hd, int page_size, float scale, int window, int min_q_long,
                                                 int* work, const float* sink_l2, cudaStream_t stream);
+BSPEC_API int bspec_attention_prefill_tc_capped(const void* q, long long q_row_stride, void* out, int* status,
+                                                long long n_pages, const void* cache, const int* qo_indptr,
+                                                const int* positions, const int* kv_indptr, const int* kv_indices,
+                                                int n_entries, long long n_tokens, int max_q_len, int Hq, int Hkv,
+                                                int hd, int page_size, float scale, int window, int min_q_long,
+                                                int* work, const float* sink_l2, float softcap, cudaStream_t stream);
 BSPEC_API int bspec_attention_prefill_tc(const void* q, long long q_row_stride, void* out, int* status,
                                          long long n_pages, const void* cache, const int* qo_indptr,
                                          const int* positions, const int* kv_indptr, const int* kv_indices,
@@ -716,7 +734,20 @@ BSPEC_API int bspec_attention_prefill_tc_masked(const void* q, long long q_row_s
                                                 int n_entries, long long n_tokens, int max_q_len, int Hq, int Hkv,
                                                 int hd, int page_size, float scale, int window, int min_q_long,
                                                 int* work, const float* sink_l2, cudaStream_t stream) {
+  return bspec_attention_prefill_tc_capped(q, q_row_stride, out, status, n_pages, cache, qo_indptr, positions, kv_indptr,
+                                           kv_indices, n_entries, n_tokens, max_q_len, Hq, Hkv, hd, page_size, scale,
+                                           window, min_q_long, work, sink_l2, 0.f, stream);
+}
+
+// The same with a soft cap c > 0 on the scaled scores (c tanh(s / c)); 0 is none.
+BSPEC_API int bspec_attention_prefill_tc_capped(const void* q, long long q_row_stride, void* out, int* status,
+                                                long long n_pages, const void* cache, const int* qo_indptr,
+                                                const int* positions, const int* kv_indptr, const int* kv_indices,
+                                                int n_entries, long long n_tokens, int max_q_len, int Hq, int Hkv,
+                                                int hd, int page_size, float scale, int window, int min_q_long,
+                                                int* work, const float* sink_l2, float softcap, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return 0;
+  if (softcap < 0.f || !(scale > 0.f)) return (int)cudaErrorInvalidValue;
   if (hd != HD || Hq % Hkv != 0 || page_size % 8 != 0 || KT % page_size != 0 || status == nullptr || n_pages <= 0 ||
       n_tokens <= 0 || work == nullptr)
     return (int)cudaErrorInvalidValue;
@@ -743,7 +774,8 @@ BSPEC_API int bspec_attention_prefill_tc_masked(const void* q, long long q_row_s
   BSPEC_LAUNCH((attn_prefill_tc_kernel), dim3(grid), THREADS, smem_bytes(), stream, kv_map, q_map,
                (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, status, qo_indptr, positions, kv_indptr,
                kv_indices, Hq, Hkv, n_entries, (int)n_items, page_size, scale * 1.4426950408889634f, window, min_q_long,
-               q_by_tma, work, sink_l2);
+               q_by_tma, work, sink_l2, softcap > 0.f ? softcap / scale : 0.f,
+               softcap > 0.f ? 2.f * scale * 1.4426950408889634f / softcap : 0.f);
   return BSPEC_LAUNCH_CHECK();
 }
 

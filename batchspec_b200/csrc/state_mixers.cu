@@ -60,9 +60,10 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
 #pragma unroll
     for (int u = 0; u < NR; ++u) {
       const int x = threadIdx.x + LT_THREADS * u;
-      const int tt = x / DM, i = x % DM;
-      const bool ok = tt < cnt && i < dim;
-      const float* row = proj + (size_t)(t0 + base + (ok ? tt : 0)) * ld + (size_t)h * dim + (ok ? i : 0);
+      const int tt = x / DM, i = x % DM;                     // tt is the same for a whole warp (DM >= 32)
+      if (tt >= cnt) break;
+      const bool ok = i < dim;
+      const float* row = proj + (size_t)(t0 + base + tt) * ld + (size_t)h * dim + (ok ? i : 0);
       qn[u] = ok ? row[q_off] : 0.f;
       kn[u] = ok ? row[k_off] : 0.f;
     }
@@ -77,24 +78,35 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
   };
   if (nt > 0) fetch(0);
   float s[NR];
+  const bool vec = (dim & 3) == 0 && (reinterpret_cast<uintptr_t>(sp) & 15) == 0;
+  if (vec) {
 #pragma unroll
-  for (int m = 0; m < NR; ++m) {
-    const int i = 32 * (m >> 2) + 4 * r + (m & 3);
-    s[m] = (live && i < dim) ? sp[i] : 0.f;
+    for (int g = 0; g < NR / 4; ++g) {
+      const int i = 32 * g + 4 * r;
+      const float4 v4 = (live && i < dim) ? *reinterpret_cast<const float4*>(sp + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      s[4 * g] = v4.x, s[4 * g + 1] = v4.y, s[4 * g + 2] = v4.z, s[4 * g + 3] = v4.w;
+    }
+  } else {
+#pragma unroll
+    for (int m = 0; m < NR; ++m) {
+      const int i = 32 * (m >> 2) + 4 * r + (m & 3);
+      s[m] = (live && i < dim) ? sp[i] : 0.f;
+    }
   }
   for (int base = 0; base < nt; base += LT_TT) {
     const int cnt = min(LT_TT, nt - base);
     __syncthreads();
 #pragma unroll
-    for (int u = 0; u < NR; ++u) {
+    for (int u = 0; u < NR; ++u) {                           // rows of tokens beyond cnt are never read
       const int x = threadIdx.x + LT_THREADS * u;
-      qs[x / DM][x % DM] = silu_f(qn[u]);                    // silu(0) = 0: rows beyond dim and tokens beyond cnt
+      if (x / DM >= cnt) break;
+      qs[x / DM][x % DM] = silu_f(qn[u]);                    // silu(0) = 0: rows beyond dim
       ks[x / DM][x % DM] = silu_f(kn[u]);
     }
 #pragma unroll
     for (int u = 0; u < VR; ++u) {
       const int x = threadIdx.x + LT_THREADS * u;
-      vs[x / LT_COLS][x % LT_COLS] = silu_f(vn[u]);
+      if (x / LT_COLS < cnt) vs[x / LT_COLS][x % LT_COLS] = silu_f(vn[u]);
     }
     __syncthreads();
     if (base + LT_TT < nt) fetch(base + LT_TT);
@@ -149,7 +161,13 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
     }
   }
   bspec::pdl_launch_dependents();
-  if (live) {
+  if (live && vec) {
+#pragma unroll
+    for (int g = 0; g < NR / 4; ++g) {
+      const int i = 32 * g + 4 * r;
+      if (i < dim) *reinterpret_cast<float4*>(sp + i) = make_float4(s[4 * g], s[4 * g + 1], s[4 * g + 2], s[4 * g + 3]);
+    }
+  } else if (live) {
 #pragma unroll
     for (int m = 0; m < NR; ++m) {
       const int i = 32 * (m >> 2) + 4 * r + (m & 3);
@@ -161,7 +179,7 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
 // ---------------------------------------------------------------- selective scan
 // xz [n, ld]: columns [x: inner | z: inner] of the in-projection.  State of a request at state + slot * stride:
 // [N][inner] float32 (the scan's S, state index major), then at tail_off [(taps-1)][inner] the last inputs of the
-// convolution, oldest first.
+// convolution, oldest first.  a2t [N][inner] float32: A[c, n] log2(e) with A = -exp(A_log), made once from the weights.
 
 // xc[t, c] = silu(bias[c] + sum_j conv[c, j] * x[t - (taps-1) + j, c]); one thread per (token, channel).
 template <typename T>
@@ -193,17 +211,24 @@ constexpr int SC_THREADS = 128;
 constexpr int SC_TT = 8;
 constexpr int SC_MAX_N = 256;
 
-// LN lanes per channel; lane l keeps states l, l + LN, ... (NPL of them) of its channel in registers.
+// LN lanes per channel; lane l keeps states l, l + LN, ... (NPL of them) of its channel in registers.  Tokens go
+// SC_TT at a time: the next batch's B and C rows and the channel's own x, dt and z are fetched into registers while
+// the recurrence runs over the current batch, and softplus and silu are taken once per batch outside the chain, so
+// what is left per token is one exponential and two multiply-adds per state.  Every token's arithmetic is the same
+// wherever it falls in a batch, so a position's result does not depend on where a portion was cut.
 template <typename T, int NPL, int LN>
 __global__ void __launch_bounds__(SC_THREADS)
 selective_scan_kernel(const float* __restrict__ xz, long long ld, const float* __restrict__ xc,
                       const float* __restrict__ dt_raw, const float* __restrict__ bc, long long ld_bc,
-                      const void* __restrict__ a_log, const void* __restrict__ dvec, const void* __restrict__ dt_bias,
+                      const float* __restrict__ a2t, const void* __restrict__ dvec, const void* __restrict__ dt_bias,
                       int w_dtype, float* __restrict__ state, long long state_stride, long long tail_off,
                       const int* __restrict__ qo_indptr, const int* __restrict__ state_slots, T* __restrict__ out,
                       long long out_stride, float out_scale, int inner, int N, int taps) {
   bspec::pdl_prologue_late(67);
-  __shared__ float bcs[SC_TT][2 * SC_MAX_N];
+  constexpr int NS = NPL * LN;                               // states this instance covers (N <= NS)
+  constexpr int BCR = SC_TT * 2 * NS / SC_THREADS;           // staged B and C values per thread and batch
+  static_assert(SC_TT * 2 * NS % SC_THREADS == 0, "the staged rows divide among the threads");
+  __shared__ __align__(16) float bcs[SC_TT][2 * NS];         // [B: NS | C: NS] of a token, zeros beyond N
   const int e = blockIdx.y;
   const int lane = threadIdx.x % LN;
   const int c = blockIdx.x * (SC_THREADS / LN) + threadIdx.x / LN;
@@ -211,44 +236,91 @@ selective_scan_kernel(const float* __restrict__ xz, long long ld, const float* _
   const int cc = live ? c : 0;
   const int t0 = qo_indptr[e], nt = qo_indptr[e + 1] - t0;
   float* sp = state + (size_t)state_slots[e] * state_stride;
+  float xn[SC_TT], dn[SC_TT], zn[SC_TT], bn[BCR];
+  auto fetch = [&](int base) {
+    const int cnt = min(SC_TT, nt - base);
+#pragma unroll
+    for (int tt = 0; tt < SC_TT; ++tt) {
+      if (tt >= cnt) break;
+      const size_t t = (size_t)(t0 + base + tt);
+      xn[tt] = xc[t * inner + cc];
+      dn[tt] = dt_raw[t * inner + cc];
+      zn[tt] = xz[t * ld + inner + cc];
+    }
+#pragma unroll
+    for (int u = 0; u < BCR; ++u) {
+      const int x = threadIdx.x + SC_THREADS * u;
+      const int tt = x / (2 * NS), k = x % (2 * NS);
+      const int n = k % NS;
+      const bool ok = tt < cnt && n < N;
+      bn[u] = ok ? bc[(size_t)(t0 + base + tt) * ld_bc + (k < NS ? n : N + n)] : 0.f;
+    }
+  };
+  if (nt > 0) fetch(0);
   float s[NPL], a2[NPL];
 #pragma unroll
   for (int m = 0; m < NPL; ++m) {
     const int n = lane + LN * m;
     const bool has = live && n < N;
     s[m] = has ? sp[(size_t)n * inner + cc] : 0.f;
-    // exp(dt A) = 2^(dt A log2 e)
-    a2[m] = has ? -expf(load_as_f32(a_log, w_dtype, (size_t)cc * N + n)) * 1.4426950408889634f : 0.f;
+    a2[m] = has ? a2t[(size_t)n * inner + cc] : 0.f;          // exp(dt A) = 2^(dt A log2 e)
   }
   const float dskip = load_as_f32(dvec, w_dtype, cc), dtb = load_as_f32(dt_bias, w_dtype, cc);
   for (int base = 0; base < nt; base += SC_TT) {
     const int cnt = min(SC_TT, nt - base);
+    float xv[SC_TT], dv[SC_TT], gv[SC_TT];
     __syncthreads();
-    for (int x = threadIdx.x; x < cnt * 2 * N; x += blockDim.x) {
-      const int tt = x / (2 * N), k = x - tt * 2 * N;
-      bcs[tt][k] = bc[(size_t)(t0 + base + tt) * ld_bc + k];
+#pragma unroll
+    for (int u = 0; u < BCR; ++u) {
+      const int x = threadIdx.x + SC_THREADS * u;
+      bcs[x / (2 * NS)][x % (2 * NS)] = bn[u];
+    }
+#pragma unroll
+    for (int tt = 0; tt < SC_TT; ++tt) {
+      if (tt >= cnt) break;
+      xv[tt] = xn[tt];
+      dv[tt] = softplus_f(dn[tt] + dtb);
+      gv[tt] = silu_f(zn[tt]) * out_scale;
     }
     __syncthreads();
-    for (int tt = 0; tt < cnt; ++tt) {
-      const size_t t = (size_t)(t0 + base + tt);
-      const float x = xc[t * inner + cc];
-      const float dt = softplus_f(dt_raw[t * inner + cc] + dtb);
-      const float dx = dt * x;
+    if (base + SC_TT < nt) fetch(base + SC_TT);
+    // one token; the same arithmetic in a whole batch (unrolled without branches, so that the tokens' independent
+    // work interleaves) and in a last, partial one
+    auto token = [&](int tt, float xt, float dt, float gt) {
+      const float dx = dt * xt;
       float y = 0.f;
+      if constexpr (LN == 1 && NPL % 4 == 0) {
 #pragma unroll
-      for (int m = 0; m < NPL; ++m) {
-        const int n = lane + LN * m;
-        if (n < N) {
-          s[m] = exp2f(dt * a2[m]) * s[m] + dx * bcs[tt][n];
-          y += s[m] * bcs[tt][N + n];
+        for (int g = 0; g < NPL / 4; ++g) {
+          const float4 b4 = *reinterpret_cast<const float4*>(&bcs[tt][4 * g]);
+          const float4 c4 = *reinterpret_cast<const float4*>(&bcs[tt][NS + 4 * g]);
+          const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, cv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            s[4 * g + q] = __fmaf_rn(exp2f(__fmul_rn(dt, a2[4 * g + q])), s[4 * g + q], __fmul_rn(dx, bb[q]));
+            y = __fmaf_rn(s[4 * g + q], cv[q], y);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < NPL; ++m) {
+          const int n = lane + LN * m;                       // states beyond N: a2 = 0, B = C = 0, s stays 0
+          s[m] = __fmaf_rn(exp2f(__fmul_rn(dt, a2[m])), s[m], __fmul_rn(dx, bcs[tt][n]));
+          y = __fmaf_rn(s[m], bcs[tt][NS + n], y);
         }
       }
 #pragma unroll
       for (int o = 1; o < LN; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-      if (live && lane == 0) {
-        const float z = xz[t * ld + inner + cc];
-        out[t * out_stride + cc] = from_f32<T>((y + dskip * x) * silu_f(z) * out_scale);
-      }
+      if (live && lane == 0)
+        out[(size_t)(t0 + base + tt) * out_stride + cc] = from_f32<T>(__fmul_rn(__fmaf_rn(dskip, xt, y), gt));
+    };
+    if (cnt == SC_TT) {
+#pragma unroll
+      for (int tt = 0; tt < SC_TT; ++tt) token(tt, xv[tt], dv[tt], gv[tt]);
+    } else {
+#pragma unroll
+      for (int tt = 0; tt < SC_TT; ++tt)
+        if (tt < cnt) token(tt, xv[tt], dv[tt], gv[tt]);
     }
   }
   bspec::pdl_launch_dependents();
@@ -304,22 +376,29 @@ BSPEC_API int bspec_scan_conv(const float* xz, long long ld, const void* conv, c
 }
 
 BSPEC_API int bspec_selective_scan(const float* xz, long long ld, const float* xc, const float* dt_raw, const float* bc,
-                                   long long ld_bc, const void* a_log, const void* dvec, const void* dt_bias,
+                                   long long ld_bc, const float* a2t, const void* dvec, const void* dt_bias,
                                    int w_dtype, float* state, long long state_stride, long long tail_off,
                                    const int* qo_indptr, const int* state_slots, void* out, int out_dtype,
                                    long long out_stride, float out_scale, int n_entries, int inner, int N, int taps,
                                    cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if (inner <= 0 || N <= 0 || N > SC_MAX_N || taps < 1 || n_entries > 65535) return (int)cudaErrorInvalidValue;
+  // few channels x requests: more lanes per channel, so that a lone prompt's chain is shorter and more SMs take part
+  const bool few = (long long)((inner + SC_THREADS - 1) / SC_THREADS) * n_entries < 148;
 #define LS(T, NPL, LN)                                                                                               \
   BSPEC_LAUNCH_SERIALIZED((selective_scan_kernel<T, NPL, LN>),                                                       \
                           dim3((inner + SC_THREADS / LN - 1) / (SC_THREADS / LN), n_entries), SC_THREADS, 0, stream, \
-                          xz, ld, xc, dt_raw, bc, ld_bc, a_log, dvec, dt_bias, w_dtype, state, state_stride, tail_off, \
+                          xz, ld, xc, dt_raw, bc, ld_bc, a2t, dvec, dt_bias, w_dtype, state, state_stride, tail_off, \
                           qo_indptr, state_slots, (T*)out, out_stride, out_scale, inner, N, taps)
 #define LSN(T)                                                                                                       \
   do {                                                                                                               \
-    if (N <= 16) LS(T, 16, 1); else if (N <= 32) LS(T, 32, 1); else if (N <= 64) LS(T, 32, 2);                       \
-    else if (N <= 128) LS(T, 32, 4); else LS(T, 32, 8);                                                              \
+    if (few) {                                                                                                       \
+      if (N <= 16) LS(T, 4, 4); else if (N <= 32) LS(T, 8, 4); else if (N <= 64) LS(T, 8, 8);                        \
+      else if (N <= 128) LS(T, 16, 8); else LS(T, 32, 8);                                                            \
+    } else {                                                                                                         \
+      if (N <= 16) LS(T, 16, 1); else if (N <= 32) LS(T, 32, 1); else if (N <= 64) LS(T, 32, 2);                     \
+      else if (N <= 128) LS(T, 32, 4); else LS(T, 32, 8);                                                            \
+    }                                                                                                                \
   } while (0)
   if (out_dtype == BSPEC_F32) LSN(float); else LSN(__nv_bfloat16);
 #undef LSN

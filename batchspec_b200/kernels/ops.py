@@ -121,6 +121,9 @@ _SIGNATURES = {
     "bspec_attention_prefill_tc_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int,
                                           c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "bspec_attention_prefill_tc_capped": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int,
+                                          c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "bspec_gemm_tc_clamped_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int,
@@ -658,8 +661,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
     on the tensor-core kernels; everything else on the generic float32-math kernel.
     ``window`` > 0 keeps the last ``window`` keys, ``chunk`` > 0 the keys of the query's own chunk of ``chunk``
     positions (one of the two at most).  ``sink`` (float32 per query head, with ``sink_l2`` its ``sink_table``) adds
-    exp(sink) to the softmax denominator.  ``softcap`` c > 0 turns a scaled score s into c tanh(s / c) (the tcgen05
-    prompt kernel knows no cap; capped layers run on the other tensor-core kernels)."""
+    exp(sink) to the softmax denominator.  ``softcap`` c > 0 turns a scaled score s into c tanh(s / c)."""
     _require_cuda(qkv, out, cache, sink, sink_l2)
     assert qkv.stride(1) == 1 and out.is_contiguous() and out.dtype == qkv.dtype == cache.dtype
     assert not (window and chunk) and window >= 0 and chunk >= 0
@@ -676,13 +678,14 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
             plan = ctx.extras[key] = _attention_plan(qkv.device, ctx, tables, n_heads, n_kv_heads, head_dim)
         (tma, balanced, n_splits, short, run_decode, run_prefill, prefill_tc, o_part, ml_part, counters, status, qo, pos,
          tok_entry, kv_indptr, kv_indices, kv_len) = plan
-        if prefill_tc and not softcap:
+        if prefill_tc:
             # long portions on the tcgen05 kernel; what is left for the call below are the short requests
-            _check(lib.bspec_attention_prefill_tc_masked(
+            _check(lib.bspec_attention_prefill_tc_capped(
                 qkv.data_ptr(), qkv.stride(0), out.data_ptr(), status, cache.shape[0], cache.data_ptr(), qo, pos,
                 kv_indptr, kv_indices, ctx.n_entries, qkv.shape[0], ctx.max_q_len, n_heads, n_kv_heads, head_dim,
                 tables.page_size,
-                float(scale), mask, short + 1, _work_counter(qkv.device).data_ptr(), _ptr(sink_l2), _stream()),
+                float(scale), mask, short + 1, _work_counter(qkv.device).data_ptr(), _ptr(sink_l2), float(softcap),
+                _stream()),
                 "attention_prefill_tc")
             run_prefill = 0
             if not run_decode:
@@ -861,28 +864,40 @@ def scan_conv(xz: torch.Tensor, conv: torch.Tensor, bias: torch.Tensor, state: t
     return xc, xr
 
 
+def scan_decay_table(a_log: torch.Tensor) -> torch.Tensor:
+    """What the scan kernel reads instead of ``a_log`` [inner, N]: A log2(e) with A = -exp(a_log), float32, laid out
+    [N, inner] like the state, so that exp(dt A) is one multiplication and one 2^x per state and token.  Made once
+    when the weights are bound."""
+    return (-torch.exp(a_log.to(torch.float32)) * 1.4426950408889634).t().contiguous()
+
+
 def selective_scan(xz: torch.Tensor, xc: torch.Tensor, dt_raw: torch.Tensor, bc: torch.Tensor, a_log: torch.Tensor,
                    d_skip: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, tail_off: int, ctx,
-                   out: torch.Tensor, out_scale: float, inner: int, n_state: int, taps: int) -> None:
+                   out: torch.Tensor, out_scale: float, inner: int, n_state: int, taps: int,
+                   decay_table: Optional[torch.Tensor] = None) -> None:
     """The selective scan over every entry's portion.  Per channel c and state n, with dt = softplus(dt_raw + dt_bias)
     and A = -exp(a_log): S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n; y_c = sum_n S[c, n] C_n + D_c x_c;
     out[t, c] = y_c silu(z_c) out_scale.  ``xz`` float32 [n, >= 2 inner] = [x before the convolution | z]; ``xc``
     float32 [n, inner] after it; ``bc`` float32 [n, 2 N] = [B | C]; ``state[slot]`` = [S as [N, inner] | the
     convolution's last taps-1 inputs at ``tail_off``], read and written.  ``out``: a view [n, inner] of rows that may
-    be wider, float32 or bfloat16."""
-    _require_cuda(xz, xc, dt_raw, bc, a_log, d_skip, dt_bias, state, out)
+    be wider, float32 or bfloat16.  ``decay_table``: ``scan_decay_table(a_log)`` kept by the caller (made here when
+    absent)."""
+    if decay_table is None:
+        decay_table = scan_decay_table(a_log)
+    _require_cuda(xz, xc, dt_raw, bc, decay_table, d_skip, dt_bias, state, out)
     n = xz.shape[0]
     f32 = torch.float32
     assert xz.dtype == f32 and xz.stride(1) == 1 and xz.shape[1] >= 2 * inner
     assert xc.dtype == f32 and xc.is_contiguous() and xc.shape == (n, inner)
     assert dt_raw.dtype == f32 and dt_raw.is_contiguous() and dt_raw.shape == (n, inner)
     assert bc.dtype == f32 and bc.stride(1) == 1 and bc.shape == (n, 2 * n_state)
-    assert a_log.shape == (inner, n_state) and a_log.is_contiguous() and a_log.dtype == d_skip.dtype == dt_bias.dtype
+    assert decay_table.shape == (n_state, inner) and decay_table.is_contiguous() and decay_table.dtype == f32
+    assert d_skip.dtype == dt_bias.dtype and d_skip.numel() == dt_bias.numel() == inner
     assert state.dtype == f32 and tail_off >= n_state * inner and tail_off + (taps - 1) * inner <= state.shape[1]
     assert out.shape == (n, inner) and out.stride(1) == 1
     _check(load_library().bspec_selective_scan(
-        xz.data_ptr(), xz.stride(0), xc.data_ptr(), dt_raw.data_ptr(), bc.data_ptr(), bc.stride(0), a_log.data_ptr(),
-        d_skip.data_ptr(), dt_bias.data_ptr(), _dtype_code(a_log.dtype), state.data_ptr(), state.stride(0),
+        xz.data_ptr(), xz.stride(0), xc.data_ptr(), dt_raw.data_ptr(), bc.data_ptr(), bc.stride(0),
+        decay_table.data_ptr(), d_skip.data_ptr(), dt_bias.data_ptr(), _dtype_code(d_skip.dtype), state.data_ptr(), state.stride(0),
         int(tail_off), ctx.qo_indptr.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(), _dtype_code(out.dtype),
         out.stride(0), float(out_scale), ctx.n_entries, inner, n_state, taps, _stream()), "selective_scan")
 

@@ -54,6 +54,7 @@ class SelectiveScan(Mixer):
         self.w_x_bc = params["x"][self.dt_rank:].contiguous()
         self.w_dt = params["dt"].contiguous()
         self.dt_bias, self.a_log, self.d_skip = f32(params["dt_bias"]), f32(params["A_log"]), f32(params["D"])
+        self.decay_table = ops.scan_decay_table(self.a_log)     # A log2(e) as [N, inner], read by the scan kernel
 
     @property
     def out_width(self) -> int:
@@ -84,5 +85,5 @@ class SelectiveScan(Mixer):
             dt_raw = ops.linear(dt_low, self.w_dt, out_dtype=torch.float32)
         with bucket("scan.recurrence"):
             ops.selective_scan(xz, xc, dt_raw, bc, self.a_log, self.d_skip, self.dt_bias, cache.state, self.tail_off,
-                               ctx, out, out_scale, self.inner, self.n_state, self.taps)
+                               ctx, out, out_scale, self.inner, self.n_state, self.taps, self.decay_table)
         return out

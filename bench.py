@@ -583,7 +583,7 @@ def tokolorn_kernels_alone(z, pk, iters=20):
         cache = torch.randn(B * pages_per, 2, ps * G * hd, device=dev).bfloat16()
         q = torch.randn(n, Hq * hd, device=dev).bfloat16()
         o = torch.empty(n, Hq * hd, device=dev, dtype=torch.bfloat16)
-        for label, win, ck, sk, sk2, cap in (("window_cap", z["window"], 0, None, None, 30.0),
+        for label, win, ck, sk, sk2, cap in (("window_cap", z["window"], 0, None, None, 50.0),
                                              ("window", z["window"], 0, None, None, 0.0),
                                              ("chunk_sink", 0, z["chunk"], sink, sink_l2, 0.0), ("causal", 0, 0, None, None, 0.0)):
             ctx.extras = {"min_q_len": min(q_lens)}
@@ -610,7 +610,7 @@ def tokolorn_kernels_alone(z, pk, iters=20):
     resid = torch.zeros(n, z["width"], device=dev)
     table = torch.randn(65522, z["width"], device=dev).bfloat16()
     prev = torch.zeros(4, 1, dtype=torch.int32, device=dev)
-    ms = _time(lambda: ops.bigram_add(resid, table, prev, ctx, 65521, 31, 7, 32000), iters)
+    ms = _time(lambda: ops.bigram_add(resid, table, prev, ctx, 65521, 1009, 17, 32000), iters)
     nbytes = n * z["width"] * (4 + 4 + 2)
     out["bigram_add_4096"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
     # the two recurrences
@@ -644,7 +644,8 @@ def tokolorn_kernels_alone(z, pk, iters=20):
         xc, _ = ops.scan_conv(xz, conv, conv_b, sstate, N * inner, ctx, inner, taps, torch.bfloat16)
         dt_raw, bc = torch.randn(n, inner, device=dev), torch.randn(n, 2 * N, device=dev)
         y = torch.empty(n, inner, device=dev, dtype=torch.bfloat16)
-        ms_s = _time(lambda: ops.selective_scan(xz, xc, dt_raw, bc, a_log, d_skip, dt_b, sstate, N * inner, ctx, y, 0.5, inner, N, taps), iters)
+        table = ops.scan_decay_table(a_log)
+        ms_s = _time(lambda: ops.selective_scan(xz, xc, dt_raw, bc, a_log, d_skip, dt_b, sstate, N * inner, ctx, y, 0.5, inner, N, taps, table), iters)
         rec = dict(conv_ms=round(ms_c, 4), scan_ms=round(ms_s, 4),
                    conv_frac_of_measured=round(n * inner * (4 + 4 + 2) / ms_c / 1e6 / pk["hbm_gbs"], 4))
         nbytes = B * inner * N * 4 * 2 + n * inner * (4 * 4 + 2)          # state once; x, z, xc, dt read, y written

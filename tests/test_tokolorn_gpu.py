@@ -66,8 +66,8 @@ CFG_B = _config(513, 100, 1e-6, [_attention(2, 1, 6, 0.4, None, ff=36),
                                  _parallel(3, 3, 10, 10, 0.3, None, None, None, None, 36, 40, 7, 1, 1.0, 1.5, ff=44),
                                  _lightning(1, 6, 40, (0.95,))], loop=(1, 3, 2), bigram=(17, 1000003, 1), embed_scale=1.0,
                 logit_scale=1.0)
-CFG_C = _config(640, 256, 1e-5, [_parallel(8, 2, 64, 64, 0.125, 128, 64, 100000.0, 30.0, 128, 16, 8, 4, 0.7, 0.4, ff=192),
-                                 _lightning(4, 64, 64, (0.7, 0.9, 0.97, 0.999), ff=192),
+CFG_C = _config(640, 320, 1e-5, [_parallel(8, 2, 64, 64, 0.125, 128, 64, 100000.0, 25.0, 128, 16, 8, 4, 0.7, 0.4, ff=192),
+                                 _lightning(5, 64, 64, (0.7, 0.9, 0.97, 0.999, 0.8), ff=192),
                                  _attention(8, 4, 64, 0.125, 64, ff=192)])
 # one layer each, no bigram rows: a changed token reaches other positions through the mixer alone
 CFG_WINDOW = _config(150, 32, 1e-5, [_parallel(2, 1, 16, 8, 0.5, 12, 16, 1000.0, 8.0, 8, 4, 2, 2, 1.0, 0.0, ff=24)],
