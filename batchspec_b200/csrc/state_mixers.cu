@@ -22,8 +22,9 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // ---------------------------------------------------------------- lightning attention
-// Block: COLS value columns of one head of one request, 8 lanes per column; lane r of a column keeps rows
-// 32 g + 4 r + e (e < 4, g < NR / 4) of that column of S in registers, so that a lane reads its four rows of q and k
+// Block: COLS value columns of one head of one request, L lanes per column (8, 16 or 32: more lanes mean more warps
+// per SM to hide the chain's latencies, and fewer rows per lane); lane r of a column keeps rows
+// 4 L g + 4 r + e (e < 4, g < NR / 4) of that column of S in registers, so that a lane reads its four rows of q and k
 // from shared memory in one 16-byte load.  Tokens are staged TT at a time in shared memory: the raw projection
 // columns of the next TT tokens are fetched into registers while the recurrence runs over the current ones, so the
 // memory latency is paid once per kernel and not once per batch of tokens.  The recurrence takes four tokens per
@@ -32,22 +33,23 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 // State of a request: [H][vdim][dim] float32 at state + slot * state_stride.
 constexpr int LT_COLS = 16;
 constexpr int LT_TT = 16;
-constexpr int LT_THREADS = LT_COLS * 8;
 
-template <int NR>
-__global__ void __launch_bounds__(LT_THREADS)
+template <int NR, int L>
+__global__ void __launch_bounds__(LT_COLS * L)
 lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_off, int k_off, int v_off,
                             const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
                             const int* __restrict__ qo_indptr, const int* __restrict__ state_slots,
                             float* __restrict__ out, int H, int dim, int vdim) {
   bspec::pdl_prologue_late(65);
-  constexpr int DM = 8 * NR;                                // rows of S this instance holds (dim <= DM)
-  constexpr int VR = LT_TT * LT_COLS / LT_THREADS;          // staged v values per thread
+  constexpr int LT_THREADS = LT_COLS * L;
+  constexpr int DM = L * NR;                                // rows of S this instance holds (dim <= DM)
+  constexpr int VR = (LT_TT * LT_COLS + LT_THREADS - 1) / LT_THREADS;          // staged v values per thread
+  static_assert(NR % 4 == 0 && (L == 8 || L == 16 || L == 32) && LT_TT * DM == NR * LT_THREADS, "lanes and rows");
   __shared__ __align__(16) float qs[LT_TT][DM];
   __shared__ __align__(16) float ks[LT_TT][DM];
   __shared__ float vs[LT_TT][LT_COLS];
   const int e = blockIdx.z, h = blockIdx.y;
-  const int col = threadIdx.x >> 3, r = threadIdx.x & 7;
+  const int col = threadIdx.x / L, r = threadIdx.x % L;
   const int j = blockIdx.x * LT_COLS + col;                 // value column of the head
   const bool live = j < vdim;
   const int t0 = qo_indptr[e], nt = qo_indptr[e + 1] - t0;
@@ -72,7 +74,7 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
       const int x = threadIdx.x + LT_THREADS * u;
       const int tt = x / LT_COLS, c = x % LT_COLS;
       const int jj = blockIdx.x * LT_COLS + c;
-      const bool ok = tt < cnt && jj < vdim;
+      const bool ok = x < LT_TT * LT_COLS && tt < cnt && jj < vdim;
       vn[u] = ok ? proj[(size_t)(t0 + base + tt) * ld + v_off + (size_t)h * vdim + jj] : 0.f;
     }
   };
@@ -82,14 +84,14 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
   if (vec) {
 #pragma unroll
     for (int g = 0; g < NR / 4; ++g) {
-      const int i = 32 * g + 4 * r;
+      const int i = 4 * L * g + 4 * r;
       const float4 v4 = (live && i < dim) ? *reinterpret_cast<const float4*>(sp + i) : make_float4(0.f, 0.f, 0.f, 0.f);
       s[4 * g] = v4.x, s[4 * g + 1] = v4.y, s[4 * g + 2] = v4.z, s[4 * g + 3] = v4.w;
     }
   } else {
 #pragma unroll
     for (int m = 0; m < NR; ++m) {
-      const int i = 32 * (m >> 2) + 4 * r + (m & 3);
+      const int i = 4 * L * (m >> 2) + 4 * r + (m & 3);
       s[m] = (live && i < dim) ? sp[i] : 0.f;
     }
   }
@@ -106,7 +108,7 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
 #pragma unroll
     for (int u = 0; u < VR; ++u) {
       const int x = threadIdx.x + LT_THREADS * u;
-      if (x / LT_COLS < cnt) vs[x / LT_COLS][x % LT_COLS] = silu_f(vn[u]);
+      if (x < LT_TT * LT_COLS && x / LT_COLS < cnt) vs[x / LT_COLS][x % LT_COLS] = silu_f(vn[u]);
     }
     __syncthreads();
     if (base + LT_TT < nt) fetch(base + LT_TT);
@@ -121,8 +123,8 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
         float4 k4[4], q4[4];
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
-          k4[a] = *reinterpret_cast<const float4*>(&ks[tt + a][32 * g + 4 * r]);
-          q4[a] = *reinterpret_cast<const float4*>(&qs[tt + a][32 * g + 4 * r]);
+          k4[a] = *reinterpret_cast<const float4*>(&ks[tt + a][4 * L * g + 4 * r]);
+          q4[a] = *reinterpret_cast<const float4*>(&qs[tt + a][4 * L * g + 4 * r]);
         }
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
@@ -135,7 +137,7 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
         }
       }
 #pragma unroll
-      for (int o = 1; o < 8; o <<= 1)
+      for (int o = 1; o < L; o <<= 1)
 #pragma unroll
         for (int a = 0; a < 4; ++a) acc[a] += __shfl_xor_sync(0xffffffffu, acc[a], o);
       const float mine = r == 0 ? acc[0] : (r == 1 ? acc[1] : (r == 2 ? acc[2] : acc[3]));
@@ -146,8 +148,8 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
       float acc = 0.f;
 #pragma unroll
       for (int g = 0; g < NR / 4; ++g) {
-        const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][32 * g + 4 * r]);
-        const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][32 * g + 4 * r]);
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][4 * L * g + 4 * r]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][4 * L * g + 4 * r]);
         const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -156,7 +158,7 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
         }
       }
 #pragma unroll
-      for (int o = 1; o < 8; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      for (int o = 1; o < L; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (live && r == 0) orow[(size_t)tt * H * vdim] = acc;
     }
   }
@@ -164,13 +166,13 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
   if (live && vec) {
 #pragma unroll
     for (int g = 0; g < NR / 4; ++g) {
-      const int i = 32 * g + 4 * r;
+      const int i = 4 * L * g + 4 * r;
       if (i < dim) *reinterpret_cast<float4*>(sp + i) = make_float4(s[4 * g], s[4 * g + 1], s[4 * g + 2], s[4 * g + 3]);
     }
   } else if (live) {
 #pragma unroll
     for (int m = 0; m < NR; ++m) {
-      const int i = 32 * (m >> 2) + 4 * r + (m & 3);
+      const int i = 4 * L * (m >> 2) + 4 * r + (m & 3);
       if (i < dim) sp[i] = s[m];
     }
   }
@@ -349,10 +351,16 @@ BSPEC_API int bspec_lightning_recurrence(const float* proj, long long ld, int q_
   if (dim <= 0 || dim > 256 || vdim <= 0 || H <= 0 || H > 65535 || n_entries > 65535)
     return (int)cudaErrorInvalidValue;
   const dim3 grid((vdim + LT_COLS - 1) / LT_COLS, H, n_entries);
-#define LL(NR)                                                                                                     \
-  BSPEC_LAUNCH_SERIALIZED((lightning_recurrence_kernel<NR>), grid, LT_THREADS, 0, stream, proj, ld, q_off, k_off, \
-                          v_off, decay, state, state_stride, qo_indptr, state_slots, out, H, dim, vdim)
-  if (dim <= 32) LL(4); else if (dim <= 64) LL(8); else if (dim <= 128) LL(16); else LL(32);
+  // few blocks (a lone prompt): 32 lanes per column, so that an SM holds 16 warps of its one block; many blocks
+  // (a decode batch): 8 lanes with more rows each, and the SMs fill with blocks
+  const bool few = (long long)grid.x * grid.y * grid.z < 4 * 148;
+#define LL(NR, L)                                                                                                  \
+  BSPEC_LAUNCH_SERIALIZED((lightning_recurrence_kernel<NR, L>), grid, LT_COLS * L, 0, stream, proj, ld, q_off,     \
+                          k_off, v_off, decay, state, state_stride, qo_indptr, state_slots, out, H, dim, vdim)
+  if (dim <= 32) LL(4, 8);
+  else if (dim <= 64) { if (few) LL(4, 16); else LL(8, 8); }
+  else if (dim <= 128) { if (few) LL(4, 32); else LL(16, 8); }
+  else { if (few) LL(8, 32); else LL(32, 8); }
 #undef LL
   return BSPEC_LAUNCH_CHECK();
 }
