@@ -20,6 +20,19 @@ namespace {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+// S <- exp(x) S + b as S + ((exp(x) - 1) S + b).  A state with a long memory has exp(x) within 1e-4 of 1, where a
+// float32 factor keeps only three digits of what matters, 1 - exp(x); taken a thousand times that shows in the sum.
+// exp(x) - 1 keeps all its digits, and the state moves by the small difference.
+// Near zero exp(x) - 1 is the series up to x^4 / 24 (the next term is below 1e-8 of the sum for |x| < 1/32); further
+// out 2^(x log2 e) - 1, whose difference from 1 is large enough to keep its digits.
+__device__ __forceinline__ float exp_minus_one(float x) {
+  const float series = __fmul_rn(x, __fmaf_rn(x, __fmaf_rn(x, __fmaf_rn(x, 1.f / 24.f, 1.f / 6.f), 0.5f), 1.f));
+  const float direct = exp2f(__fmul_rn(x, 1.4426950408889634f)) - 1.f;
+  return fabsf(x) < 0.03125f ? series : direct;
+}
+__device__ __forceinline__ float scan_update(float s, float x, float b) {
+  return __fadd_rn(s, __fmaf_rn(exp_minus_one(x), s, b));
+}
 
 // ---------------------------------------------------------------- lightning attention
 // Block: COLS value columns of one head of one request, L lanes per column (8, 16 or 32: more lanes mean more warps
@@ -181,7 +194,7 @@ lightning_recurrence_kernel(const float* __restrict__ proj, long long ld, int q_
 // ---------------------------------------------------------------- selective scan
 // xz [n, ld]: columns [x: inner | z: inner] of the in-projection.  State of a request at state + slot * stride:
 // [N][inner] float32 (the scan's S, state index major), then at tail_off [(taps-1)][inner] the last inputs of the
-// convolution, oldest first.  a2t [N][inner] float32: A[c, n] log2(e) with A = -exp(A_log), made once from the weights.
+// convolution, oldest first.  a2t [N][inner] float32: A[c, n] = -exp(A_log[c, n]), made once from the weights.
 
 // xc[t, c] = silu(bias[c] + sum_j conv[c, j] * x[t - (taps-1) + j, c]); one thread per (token, channel).
 template <typename T>
@@ -265,7 +278,7 @@ selective_scan_kernel(const float* __restrict__ xz, long long ld, const float* _
     const int n = lane + LN * m;
     const bool has = live && n < N;
     s[m] = has ? sp[(size_t)n * inner + cc] : 0.f;
-    a2[m] = has ? a2t[(size_t)n * inner + cc] : 0.f;          // exp(dt A) = 2^(dt A log2 e)
+    a2[m] = has ? a2t[(size_t)n * inner + cc] : 0.f;
   }
   const float dskip = load_as_f32(dvec, w_dtype, cc), dtb = load_as_f32(dt_bias, w_dtype, cc);
   for (int base = 0; base < nt; base += SC_TT) {
@@ -299,7 +312,7 @@ selective_scan_kernel(const float* __restrict__ xz, long long ld, const float* _
           const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, cv[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            s[4 * g + q] = __fmaf_rn(exp2f(__fmul_rn(dt, a2[4 * g + q])), s[4 * g + q], __fmul_rn(dx, bb[q]));
+            s[4 * g + q] = scan_update(s[4 * g + q], __fmul_rn(dt, a2[4 * g + q]), __fmul_rn(dx, bb[q]));
             y = __fmaf_rn(s[4 * g + q], cv[q], y);
           }
         }
@@ -307,7 +320,7 @@ selective_scan_kernel(const float* __restrict__ xz, long long ld, const float* _
 #pragma unroll
         for (int m = 0; m < NPL; ++m) {
           const int n = lane + LN * m;                       // states beyond N: a2 = 0, B = C = 0, s stays 0
-          s[m] = __fmaf_rn(exp2f(__fmul_rn(dt, a2[m])), s[m], __fmul_rn(dx, bcs[tt][n]));
+          s[m] = scan_update(s[m], __fmul_rn(dt, a2[m]), __fmul_rn(dx, bcs[tt][n]));
           y = __fmaf_rn(s[m], bcs[tt][NS + n], y);
         }
       }

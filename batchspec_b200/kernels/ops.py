@@ -865,10 +865,10 @@ def scan_conv(xz: torch.Tensor, conv: torch.Tensor, bias: torch.Tensor, state: t
 
 
 def scan_decay_table(a_log: torch.Tensor) -> torch.Tensor:
-    """What the scan kernel reads instead of ``a_log`` [inner, N]: A log2(e) with A = -exp(a_log), float32, laid out
-    [N, inner] like the state, so that exp(dt A) is one multiplication and one 2^x per state and token.  Made once
-    when the weights are bound."""
-    return (-torch.exp(a_log.to(torch.float32)) * 1.4426950408889634).t().contiguous()
+    """What the scan kernel reads instead of ``a_log`` [inner, N]: A = -exp(a_log), float32, laid out [N, inner] like
+    the state, so that a step's decay is exp(dt A) with nothing else to compute or to read from scattered places.
+    Made once when the weights are bound."""
+    return (-torch.exp(a_log.to(torch.float32))).t().contiguous()
 
 
 def selective_scan(xz: torch.Tensor, xc: torch.Tensor, dt_raw: torch.Tensor, bc: torch.Tensor, a_log: torch.Tensor,

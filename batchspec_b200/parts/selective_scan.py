@@ -54,7 +54,7 @@ class SelectiveScan(Mixer):
         self.w_x_bc = params["x"][self.dt_rank:].contiguous()
         self.w_dt = params["dt"].contiguous()
         self.dt_bias, self.a_log, self.d_skip = f32(params["dt_bias"]), f32(params["A_log"]), f32(params["D"])
-        self.decay_table = ops.scan_decay_table(self.a_log)     # A log2(e) as [N, inner], read by the scan kernel
+        self.decay_table = ops.scan_decay_table(self.a_log)     # A = -exp(A_log) as [N, inner], read by the scan kernel
 
     @property
     def out_width(self) -> int:
