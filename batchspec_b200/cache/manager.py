@@ -122,6 +122,7 @@ class RequestCache:
     length: int = 0
     tables: List[List[int]] = field(default_factory=list)   # per group: page id per logical page, -1 once released
     serial: int = 0     # which admission this is: a request that is released and admitted again gets a new one
+    dead: List[int] = field(default_factory=list)   # per group: how many leading pages were given back (all -1)
 
 
 class CacheManager:
@@ -214,7 +215,7 @@ class CacheManager:
             if st is not None:
                 st[slot].zero_()
         self._admissions = getattr(self, "_admissions", 0) + 1
-        rc = RequestCache(req_id, slot, 0, [[] for _ in self.groups], self._admissions)
+        rc = RequestCache(req_id, slot, 0, [[] for _ in self.groups], self._admissions, [0] * len(self.groups))
         self.requests[req_id] = rc
         return rc
 
@@ -282,7 +283,7 @@ class CacheManager:
         lie before the chunk of every later query."""
         rc = self.requests[req_id]
         rc.length += n_new
-        for g, table in zip(self.groups, rc.tables):
+        for gi, (g, table) in enumerate(zip(self.groups, rc.tables)):
             assert len(table) == -(-rc.length // g.page_size), "block table out of step"
             if g.spec.policy == "window":
                 first_needed = max(0, rc.length - g.spec.window + 1)
@@ -291,11 +292,11 @@ class CacheManager:
             else:
                 continue
             dead = first_needed // g.page_size             # pages wholly before first_needed
-            gone = [p for p in table[:dead] if p >= 0]
-            if gone:
-                g.pool.free(gone)
-                for i in range(dead):
-                    table[i] = -1
+            was = rc.dead[gi]                              # those before ``was`` went back at earlier commits
+            if dead > was:
+                g.pool.free(table[was:dead])
+                table[was:dead] = [-1] * (dead - was)
+                rc.dead[gi] = dead
 
     def release(self, req_id) -> None:
         rc = self.requests.pop(req_id)
@@ -316,4 +317,8 @@ class CacheManager:
             assert len(held) == g.pool.num_held, f"group {gi}: {g.pool.num_held} pages out, {len(held)} in tables"
             assert set(held).isdisjoint(g.pool._free), "a held page is on the free list"
             assert len(set(g.pool._free)) == len(g.pool._free), "a page is on the free list twice"
+        for rc in self.requests.values():
+            for table, dead in zip(rc.tables, rc.dead):
+                assert all(p < 0 for p in table[:dead]) and all(p >= 0 for p in table[dead:]), \
+                    "pages are given back from the front only"
         assert len(self.requests) == self.slots.n - self.slots.num_free

@@ -333,6 +333,34 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate
   T* op = out + ((size_t)t * H + h) * V;
   for (int j = lane; j < V; j += 32) op[j] = from_f32<T>(x[j] * r * load_as_f32(w, w_dtype, j) * (gate_kind == 1 ? 1.f / (1.f + expf(-gp[j])) : silu_f(gp[j])));
 }
+
+// The same for wide groups (all heads normed together: V in the thousands), where a warp per group would leave a
+// decode step on a handful of warps: a block of 256 threads per (token, group), the sum of squares joined through
+// shared memory in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_wide_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long gate_stride,
+                          const void* __restrict__ w, int w_dtype, T* __restrict__ out, int H, int V, float eps,
+                          int gate_kind) {
+  bspec::pdl_prologue(62);
+  __shared__ float part[8];
+  const int item = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = item / H, h = item - t * H;
+  const float* x = o + ((size_t)t * H + h) * V;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < V; j += 256) ss += x[j] * x[j];
+  ss = warp_sum(ss);
+  if (lane == 0) part[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += part[i];
+  const float r = 1.f / sqrtf(tot / (float)V + eps);
+  const float* gp = gate + (size_t)t * gate_stride + (size_t)h * V;
+  T* op = out + ((size_t)t * H + h) * V;
+  for (int j = threadIdx.x; j < V; j += 256)
+    op[j] = from_f32<T>(x[j] * r * load_as_f32(w, w_dtype, j) * (gate_kind == 1 ? 1.f / (1.f + expf(-gp[j])) : silu_f(gp[j])));
+}
 }  // namespace
 
 BSPEC_API int bspec_delta_prepare(const float* proj, int n, int ld, int b_off, int a_off, const void* conv,
@@ -380,6 +408,15 @@ BSPEC_API int bspec_gated_rmsnorm(const float* o, const float* gate, long long g
                                   void* out, int out_dtype, int n, int H, int V, float eps, int gate_kind,
                                   cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (V >= 512) {                                            // the choice rests on the group's size alone
+    if (out_dtype == BSPEC_F32)
+      BSPEC_LAUNCH((gated_rmsnorm_wide_kernel<float>), n * H, 256, 0, stream, o, gate, gate_stride, w, w_dtype,
+                   (float*)out, H, V, eps, gate_kind);
+    else
+      BSPEC_LAUNCH((gated_rmsnorm_wide_kernel<__nv_bfloat16>), n * H, 256, 0, stream, o, gate, gate_stride, w, w_dtype,
+                   (__nv_bfloat16*)out, H, V, eps, gate_kind);
+    return BSPEC_LAUNCH_CHECK();
+  }
   const int blocks = (n * H + 3) / 4;
   if (out_dtype == BSPEC_F32)
     BSPEC_LAUNCH((gated_rmsnorm_kernel<float>), blocks, 128, 0, stream, o, gate, gate_stride, w, w_dtype, (float*)out, n, H, V, eps, gate_kind);

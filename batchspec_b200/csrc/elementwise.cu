@@ -513,10 +513,41 @@ __global__ void gate_mul_kernel(const T* __restrict__ x, const float* __restrict
   }
 }
 
+// Four columns per thread (bfloat16; widths, strides and addresses that allow 8- and 16-byte accesses).
+__global__ void gate_mul_bf16x4_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gate,
+                                       long long gate_stride, __nv_bfloat16* __restrict__ out, long long out_stride,
+                                       int width, float factor) {
+  bspec::pdl_prologue(68);
+  const size_t t = blockIdx.y;
+  const int j = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+  if (j >= width) return;
+  const uint2 raw = *reinterpret_cast<const uint2*>(x + t * width + j);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  float v[4] = {__low2float(a) * factor, __high2float(a) * factor, __low2float(b) * factor, __high2float(b) * factor};
+  if (gate != nullptr) {
+    const float4 g = *reinterpret_cast<const float4*>(gate + t * gate_stride + j);
+    const float gg[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __fdividef(v[i], 1.f + __expf(-gg[i]));
+  }
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 o;
+  o.x = *reinterpret_cast<uint32_t*>(&lo);
+  o.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(out + t * out_stride + j) = o;
+}
+
 BSPEC_API int bspec_gate_mul(const void* x, const float* gate, long long gate_stride, void* out, long long out_stride,
                              int dtype, int n, int width, float factor, cudaStream_t stream) {
   if (n <= 0 || width <= 0) return 0;
   if (n > 65535 * 32) return (int)cudaErrorInvalidConfiguration;
+  if (dtype != BSPEC_F32 && n <= 65535 && width % 4 == 0 && out_stride % 4 == 0 && ((uintptr_t)x & 7) == 0 &&
+      ((uintptr_t)out & 7) == 0 && (gate == nullptr || (gate_stride % 4 == 0 && ((uintptr_t)gate & 15) == 0))) {
+    const int threads = width / 4 >= 256 ? 256 : ((width / 4 + 31) / 32) * 32;
+    BSPEC_LAUNCH(gate_mul_bf16x4_kernel, dim3((width / 4 + threads - 1) / threads, n), threads, 0, stream,
+                 (const __nv_bfloat16*)x, gate, gate_stride, (__nv_bfloat16*)out, out_stride, width, factor);
+    return BSPEC_LAUNCH_CHECK();
+  }
   const dim3 grid((width + 255) / 256, n);
   if (n > 65535) return (int)cudaErrorInvalidConfiguration;
   if (dtype == BSPEC_F32)

@@ -75,6 +75,7 @@ class DecodeGraph:
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=engine.device)
         self.row_req: List[object] = [None] * B
         self.row_pages = [[0] * ng for _ in range(B)]
+        self.row_dead = [[0] * ng for _ in range(B)]       # leading table entries of the row that are -1 on the device
         self.tables_dirty = True
         self.const_uploaded = False
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -145,15 +146,18 @@ class DecodeGraph:
                 P = self.P[g]
                 if len(table) > P:
                     raise RuntimeError(f"request {rid!r} holds {len(table)} pages, the captured step allows {P}")
+                base = off[f"kv_indices{g}"] + i * P
+                dead = rc.dead[g]
                 if fresh or len(table) != have:
-                    base = off[f"kv_indices{g}"] + i * P
                     lo = 0 if fresh or len(table) < have else have
                     m[base + lo:base + len(table)] = table[lo:]
                     self.row_pages[i][g] = len(table)
                     self.tables_dirty = True
-                elif cache.groups[g].spec.policy in ("window", "chunk"):
-                    base = off[f"kv_indices{g}"] + i * P         # released pages turn into -1 in place
-                    m[base:base + len(table)] = table
+                    if fresh or len(table) < have:
+                        self.row_dead[i][g] = dead              # the whole table was written, -1 entries included
+                if dead > self.row_dead[i][g]:                  # pages a window or a chunk gave back turn into -1
+                    m[base + self.row_dead[i][g]:base + dead] = -1
+                    self.row_dead[i][g] = dead
                     self.tables_dirty = True
             self.row_req[i] = (rid, rc.serial)
 

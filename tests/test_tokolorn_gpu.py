@@ -239,7 +239,7 @@ STEPS = [dict(a=5, b=1, c=2), dict(a=1, c=1), dict(b=11, a=2, c=1), dict(c=1), d
 
 
 @pytest.mark.parametrize("Hh,dk,dv", [(3, 8, 12), (2, 20, 7), (1, 6, 40), (4, 64, 64), (2, 128, 33), (1, 256, 16),
-                                      (8, 32, 128)])
+                                      (8, 32, 128), (6, 16, 90)])
 def test_lightning_attention_over_portions_and_reused_slots(ops, Hh, dk, dv):
     """Three requests in portions of unequal sizes (one left out of some steps) against the plain recurrence over each
     whole sequence, with the norm over all heads and the sigmoid gate; then a cleared slot is used again."""
