@@ -323,6 +323,40 @@ def test_selective_scan_over_portions_and_reused_slots(ops, inner, N, taps, out_
     assert (again - want).abs().max() <= tol * max(1.0, want.abs().max().item())
 
 
+def test_a_scan_with_a_long_memory_keeps_its_digits(ops):
+    """Decays within 1e-3 to 1e-4 of 1 over 1,500 tokens, cut into portions: a float32 factor exp(dt A) keeps two or
+    three digits of 1 - exp(dt A), and with it the read-outs end 4e-6 and more of their size away from the float64
+    scan (measured with a correctly rounded exponential); moving the state by (exp(dt A) - 1) S + b stays below 1e-6.
+    The bound lies between the two."""
+    inner, N, taps, T = 48, 16, 2, 1500
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    rnd = lambda *s: torch.randn(*s, device=DEV, generator=gen)
+    conv, conv_b = rnd(inner, taps) * 0.7, rnd(inner) * 0.3
+    a_log = torch.log(torch.full((inner, N), 0.01, device=DEV) * (1 + torch.arange(N, device=DEV)))   # A = -0.01 .. -0.16
+    d_skip, dt_b = torch.zeros(inner, device=DEV), torch.full((inner,), -5.0, device=DEV)            # dt around 0.007
+    tail_off = N * inner
+    state = torch.zeros(2, tail_off + (taps - 1) * inner, device=DEV)
+    ld = 2 * inner
+    rows = {"a": torch.cat([rnd(T, ld), rnd(T, inner) * 0.5, rnd(T, 2 * N)], dim=1)}
+
+    def run(x, ctx):
+        xz = x[:, :ld]
+        xc, _ = ops.scan_conv(xz, conv, conv_b, state, tail_off, ctx, inner, taps, torch.float32)
+        y = torch.empty(x.shape[0], inner, device=DEV)
+        ops.selective_scan(xz, xc, x[:, ld:ld + inner].contiguous(), x[:, ld + inner:], a_log, d_skip, dt_b, state,
+                           tail_off, ctx, y, 1.0, inner, N, taps)
+        return y
+
+    steps = [dict(a=700), dict(a=1), dict(a=3), dict(a=500), dict(a=1), dict(a=295)]
+    got = _feed(steps, {"a": 1}, rows, run)["a"]
+    x = rows["a"].double().cpu()
+    xc = P.silu(P.causal_conv(x[:, :inner], conv.double().cpu(), conv_b.double().cpu()))
+    dt = P.softplus(x[:, ld:ld + inner] + dt_b.double().cpu())
+    want = P.diagonal_scan(xc, dt, -torch.exp(a_log.double().cpu()), x[:, ld + inner:ld + inner + N],
+                           x[:, ld + inner + N:], d_skip.double().cpu()) * P.silu(x[:, inner:2 * inner])
+    assert (got - want).abs().max() <= 2e-6 * want.abs().max(), ((got - want).abs().max(), want.abs().max())
+
+
 def _paged_keys(dtype, G, hd, vd, ps, q_lens, kv_lens, seed, values_are_keys):
     """Random keys (and values) of every request in pages handed out in scrambled order."""
     g = torch.Generator(device=DEV).manual_seed(seed)
