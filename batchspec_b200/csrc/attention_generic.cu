@@ -31,7 +31,7 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int hd, int page_size, float scale,
                     int window, long long n_pages, int vd, int chunk, const float* __restrict__ sink,
                     float softcap, int v_is_k, const float* __restrict__ gate, long long gate_stride,
-                    long long out_stride, float out_scale) {
+                    long long out_stride, float out_scale, int gate_per_head) {
   bspec::pdl_prologue(7);
   __shared__ float qs[WARPS][MAX_HD];
   const int e = blockIdx.y, h = blockIdx.z;
@@ -109,13 +109,14 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
   }
   const float inv = 1.f / l;
   T* op = out + (size_t)t * out_stride + (size_t)h * vd;
-  const float* gp = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)h * vd : nullptr;
+  // one gate logit per output number, or (gate_per_head) one per head: row [Hq] instead of [Hq * vd]
+  const float* gp = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)h * (gate_per_head ? 1 : vd) : nullptr;
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
     const int d = lane + 32 * i;
     if (d < vd) {
       float o = acc[i] * inv;
-      if (gp != nullptr) o = o / (1.f + expf(-gp[d]));
+      if (gp != nullptr) o = o / (1.f + expf(-gp[gate_per_head ? 0 : d]));
       op[d] = from_f32<T>(o * out_scale);
     }
   }
@@ -129,7 +130,8 @@ static int launch_attention_generic(const void* q, long long q_row_stride, void*
                                     const int* kv_indices, int n_entries, int max_q_len, int Hq, int Hkv, int hd,
                                     int page_size, float scale, int window, long long n_pages, int vd, int chunk,
                                     const float* sink, float softcap, int v_is_k, const float* gate,
-                                    long long gate_stride, long long out_stride, float out_scale, cudaStream_t stream) {
+                                    long long gate_stride, long long out_stride, float out_scale, int gate_per_head,
+                                    cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return 0;
   if (v_is_k && vd != hd) return (int)cudaErrorInvalidValue;
   if (hd > MAX_HD || hd <= 0 || vd > MAX_HD || vd <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
@@ -139,12 +141,12 @@ static int launch_attention_generic(const void* q, long long q_row_stride, void*
     BSPEC_LAUNCH((attn_generic_kernel<float>), grid, WARPS * 32, 0, stream, 
         (const float*)q, q_row_stride, (float*)out, (const float*)cache, qo_indptr, positions, kv_indptr, kv_indices,
         Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink, softcap, v_is_k, gate, gate_stride, out_stride,
-        out_scale);
+        out_scale, gate_per_head);
   else
     BSPEC_LAUNCH((attn_generic_kernel<__nv_bfloat16>), grid, WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, qo_indptr, positions,
         kv_indptr, kv_indices, Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink, softcap, v_is_k, gate,
-        gate_stride, out_stride, out_scale);
+        gate_stride, out_stride, out_scale, gate_per_head);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -155,27 +157,28 @@ BSPEC_API int bspec_attention_generic(const void* q, long long q_row_stride, voi
                                       cudaStream_t stream) {
   return launch_attention_generic(q, q_row_stride, out, cache, dtype, qo_indptr, positions, kv_indptr, kv_indices,
                                   n_entries, max_q_len, Hq, Hkv, hd, page_size, scale, window, n_pages, hd, 0, nullptr,
-                                  0.f, 0, nullptr, 0, (long long)Hq * hd, 1.f, stream);
+                                  0.f, 0, nullptr, 0, (long long)Hq * hd, 1.f, 0, stream);
 }
 
 // The same with values of their own size ``vd``, a chunk mask (0: none), a sink per query head (null: none), a soft
-// cap on the scores (0: none), values that are the keys, a sigmoid gate on the output, an output scale and stride.
+// cap on the scores (0: none), values that are the keys, a sigmoid gate on the output (per number, or per head), an output scale and stride.
 BSPEC_API int bspec_attention_masked(const void* q, long long q_row_stride, void* out, const void* cache, int dtype,
                                      const int* qo_indptr, const int* positions, const int* kv_indptr,
                                      const int* kv_indices, int n_entries, int max_q_len, int Hq, int Hkv, int hd,
                                      int vd, int page_size, float scale, int window, int chunk, const float* sink,
                                      long long n_pages, float softcap, int v_is_k, const float* gate,
                                      long long gate_stride, long long out_stride, float out_scale,
-                                     cudaStream_t stream) {
+                                     int gate_per_head, cudaStream_t stream) {
   return launch_attention_generic(q, q_row_stride, out, cache, dtype, qo_indptr, positions, kv_indptr, kv_indices,
                                   n_entries, max_q_len, Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink,
-                                  softcap, v_is_k, gate, gate_stride, out_stride, out_scale, stream);
+                                  softcap, v_is_k, gate, gate_stride, out_stride, out_scale, gate_per_head, stream);
 }
 
 // ---------------------------------------------------------------- q/k/v preparation
 // From the float32 rows of the fused projection [q: Hq*hd | k: Hkv*hd | v: Hkv*vd]: add the bias (if any), rotate the
 // first ``rot`` numbers of every q and k head (pair (i, i + rot/2), or (2i, 2i+1) with ``interleaved``; cosine and
-// sine times ``magnitude``), divide every q and k head by its root mean square (``norm_eps`` > 0; none otherwise),
+// sine times ``magnitude``), divide every q and k head by its root mean square (``norm_eps`` > 0; none otherwise; times ``q_norm_w`` / ``k_norm_w``,
+// a weight per number of a head, when given; before the rotation with ``norm_first``),
 // all in float32; then write q to ``q_out`` [n, Hq*hd] and k and v into the cache page of the token's position.
 // Rows of the input have stride ``ld`` (they may hold more columns).  vd == 0: there are no values (they are the
 // keys); a page then holds keys only.  One warp per head.
@@ -207,7 +210,9 @@ qkv_prepare_kernel(const float* __restrict__ qkv, long long ld, int Hq, int Hkv,
                    int bias_dtype, const float* __restrict__ inv_freq, int rot, int interleaved, float magnitude,
                    float norm_eps, const int* __restrict__ positions, const int* __restrict__ tok_entry,
                    const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, T* __restrict__ q_out,
-                   T* __restrict__ cache, int page_size, int write_kv, long long n_pages) {
+                   T* __restrict__ cache, int page_size, int write_kv, long long n_pages,
+                   const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_w_dtype,
+                   int norm_first) {
   bspec::pdl_prologue(19);
   __shared__ __align__(16) float xs[PREP_WARPS][MAX_HD];
   __shared__ float cs[MAX_HD];                                // [rot/2] cosines, then [rot/2] sines, of this token
@@ -259,8 +264,19 @@ qkv_prepare_kernel(const float* __restrict__ qkv, long long ld, int Hq, int Hkv,
       x[d] = src[d] + (bias != nullptr ? load_as_f32(bias, bias_dtype, (size_t)col0 + d) : 0.f);
   }
   __syncwarp();
-  float ss = 0.f;
   if (!is_v) {
+    // every q and k head divided by its root mean square, times a weight per number when one is given (the same
+    // for all heads); before the rotation (norm_first) or after it
+    const void* nw = slot < Hq ? q_norm_w : k_norm_w;
+    auto normalise = [&]() {
+      float ss = 0.f;
+      for (int d = lane; d < hd; d += 32) ss += x[d] * x[d];
+      ss = warp_sum(ss);
+      const float r = 1.f / sqrtf(ss / (float)hd + norm_eps);
+      for (int d = lane; d < hd; d += 32) x[d] = x[d] * r * (nw != nullptr ? load_as_f32(nw, norm_w_dtype, d) : 1.f);
+      __syncwarp();
+    };
+    if (norm_eps > 0.f && norm_first) normalise();
     const int half = rot / 2;
     for (int j = lane; j < half; j += 32) {
       const float c = cs[j], sn = cs[half + j];
@@ -270,12 +286,9 @@ qkv_prepare_kernel(const float* __restrict__ qkv, long long ld, int Hq, int Hkv,
       x[b] = v * c + u * sn;
     }
     __syncwarp();
-    if (norm_eps > 0.f) {
-      for (int d = lane; d < hd; d += 32) ss += x[d] * x[d];
-      ss = warp_sum(ss);
-    }
+    if (norm_eps > 0.f && !norm_first) normalise();
   }
-  const float r = (!is_v && norm_eps > 0.f) ? 1.f / sqrtf(ss / (float)hd + norm_eps) : 1.f;
+  const float r = 1.f;
   T* dst = nullptr;
   if (slot < Hq) {
     dst = q_out + ((size_t)t * Hq + slot) * hd;
@@ -310,7 +323,8 @@ BSPEC_API int bspec_qkv_prepare(const float* qkv, long long ld, int n, int Hq, i
                                 int bias_dtype, const float* inv_freq, int rot, int interleaved, float magnitude,
                                 float norm_eps, const int* positions, const int* tok_entry, const int* kv_indptr,
                                 const int* kv_indices, void* q_out, void* cache, int dtype, int page_size, int write_kv,
-                                long long n_pages, cudaStream_t stream) {
+                                long long n_pages, const void* q_norm_w, const void* k_norm_w, int norm_w_dtype,
+                                int norm_first, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (hd <= 0 || hd > MAX_HD || vd < 0 || vd > MAX_HD || ld < (long long)(Hq + Hkv) * hd + (long long)Hkv * vd || rot < 0 || rot > hd || rot % 2 != 0 ||
       (rot > 0 && inv_freq == nullptr))
@@ -320,11 +334,12 @@ BSPEC_API int bspec_qkv_prepare(const float* qkv, long long ld, int n, int Hq, i
   if (dtype == BSPEC_F32)
     BSPEC_LAUNCH((qkv_prepare_kernel<float>), grid, PREP_WARPS * 32, 0, stream, qkv, ld, Hq, Hkv, hd, vd, bias, bias_dtype,
                  inv_freq, rot, interleaved, magnitude, norm_eps, positions, tok_entry, kv_indptr, kv_indices,
-                 (float*)q_out, (float*)cache, page_size, write_kv, n_pages);
+                 (float*)q_out, (float*)cache, page_size, write_kv, n_pages, q_norm_w, k_norm_w, norm_w_dtype, norm_first);
   else
     BSPEC_LAUNCH((qkv_prepare_kernel<__nv_bfloat16>), grid, PREP_WARPS * 32, 0, stream, qkv, ld, Hq, Hkv, hd, vd, bias,
                  bias_dtype, inv_freq, rot, interleaved, magnitude, norm_eps, positions, tok_entry, kv_indptr,
-                 kv_indices, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, page_size, write_kv, n_pages);
+                 kv_indices, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, page_size, write_kv, n_pages, q_norm_w, k_norm_w,
+                 norm_w_dtype, norm_first);
   return BSPEC_LAUNCH_CHECK();
 }
 

@@ -29,7 +29,8 @@ from typing import List, Optional
 CSRC = Path(__file__).resolve().parent
 LIB_NAME = "libbspec_kernels.so"
 # files that only some mixers or feed-forwards need; every other .cu file is the core
-FEATURES = {"latent": ("latent.cu", "latent_mma.cu"), "moe": ("moe.cu",), "state_mixers": ("state_mixers.cu",)}
+FEATURES = {"latent": ("latent.cu", "latent_mma.cu"), "moe": ("moe.cu",), "state_mixers": ("state_mixers.cu",),
+            "streams": ("streams.cu",)}
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]

@@ -641,45 +641,54 @@ BSPEC_API int bspec_clamped_glu(const void* u, void* m, int dtype, int n, int in
   return BSPEC_LAUNCH_CHECK();
 }
 
-// ---------------------------------------------------------------- exact GELU in place:  0.5 x (1 + erf(x / sqrt 2))
-template <typename T>
+// ---------------------------------------------------------------- activations in place
+// ACT 0: exact GELU, 0.5 x (1 + erf(x / sqrt 2));  ACT 1: the square of relu, max(x, 0)^2
+template <int ACT> __device__ __forceinline__ float act_inplace(float v) {
+  if (ACT == 1) { const float r = fmaxf(v, 0.f); return r * r; }
+  return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+}
+template <typename T, int ACT>
 __global__ void gelu_erf_kernel(T* __restrict__ x, size_t total) {
   bspec::pdl_prologue(16);
-  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-    const float v = to_f32(x[idx]);
-    x[idx] = from_f32<T>(0.5f * v * (1.f + erff(v * 0.70710678118654752440f)));
-  }
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+    x[idx] = from_f32<T>(act_inplace<ACT>(to_f32(x[idx])));
 }
 
+template <int ACT>
 __global__ void gelu_erf_bf16x8_kernel(uint4* __restrict__ x, size_t total8) {
   bspec::pdl_prologue(16);
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
     uint4 v = x[idx];
     __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float f = __bfloat162float(e[j]);
-      e[j] = __float2bfloat16_rn(0.5f * f * (1.f + erff(f * 0.70710678118654752440f)));
-    }
+    for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16_rn(act_inplace<ACT>(__bfloat162float(e[j])));
     x[idx] = v;
   }
 }
 
-BSPEC_API int bspec_gelu_erf(void* x, int dtype, long long total, cudaStream_t stream) {
+template <int ACT>
+static int launch_act_inplace(void* x, int dtype, long long total, cudaStream_t stream) {
   if (total <= 0) return 0;
   if (dtype == BSPEC_BF16 && total % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15)) {
     const size_t total8 = (size_t)total / 8;
     const size_t want8 = (total8 + 255) / 256, cap8 = (size_t)bspec::sm_count() * 16;
-    BSPEC_LAUNCH((gelu_erf_bf16x8_kernel), (int)(want8 > cap8 ? cap8 : want8), 256, 0, stream, (uint4*)x, total8);
+    BSPEC_LAUNCH((gelu_erf_bf16x8_kernel<ACT>), (int)(want8 > cap8 ? cap8 : want8), 256, 0, stream, (uint4*)x, total8);
     return BSPEC_LAUNCH_CHECK();
   }
   const int threads = 256;
   size_t want = ((size_t)total + threads - 1) / threads;
   const size_t cap = (size_t)bspec::sm_count() * 32;
   const int blocks = (int)(want > cap ? cap : want);
-  if (dtype == BSPEC_F32) BSPEC_LAUNCH((gelu_erf_kernel<float>), blocks, threads, 0, stream, (float*)x, (size_t)total);
-  else BSPEC_LAUNCH((gelu_erf_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)x, (size_t)total);
+  if (dtype == BSPEC_F32) BSPEC_LAUNCH((gelu_erf_kernel<float, ACT>), blocks, threads, 0, stream, (float*)x, (size_t)total);
+  else BSPEC_LAUNCH((gelu_erf_kernel<__nv_bfloat16, ACT>), blocks, threads, 0, stream, (__nv_bfloat16*)x, (size_t)total);
   return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_gelu_erf(void* x, int dtype, long long total, cudaStream_t stream) {
+  return launch_act_inplace<0>(x, dtype, total, stream);
+}
+BSPEC_API int bspec_relu_squared(void* x, int dtype, long long total, cudaStream_t stream) {
+  return launch_act_inplace<1>(x, dtype, total, stream);
 }
 
 // ---------------------------------------------------------------- soft cap in place:  cap * tanh(x / cap)

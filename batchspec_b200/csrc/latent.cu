@@ -3,7 +3,8 @@
 // is [ql | qr], ql its unrotated query already multiplied by the head's key up-projection (R numbers) and qr its
 // rotated part (P numbers); score(i, j) = scale * ([ql | qr] . entry_j), causal softmax, and the head's output
 // is sum_j p_j c_j (R numbers), which the caller multiplies by the head's value up-projection.  All heads read the
-// same entries.
+// same entries.  ``window`` > 0: a query sees its own entry and the window - 1 before it; ``sink``: a logit per head
+// whose exponential joins the softmax denominator (no key, no value, not scaled).
 //
 // Kernels here:
 //   latent_prepare      per token: RMS norm of the query latent, RMS norm of the key/value latent, rotation of kr
@@ -86,7 +87,7 @@ latent_attn_generic_kernel(const T* __restrict__ ql, long long ql_row, long long
                            const T* __restrict__ cache, const int* __restrict__ qo_indptr,
                            const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                            const int* __restrict__ kv_indices, int H, int R, int P, int page_size, float scale,
-                           long long n_pages) {
+                           long long n_pages, int window, const float* __restrict__ sink) {
   bspec::pdl_prologue(41);
   extern __shared__ float qs_all[];
   const int D = R + P;
@@ -106,9 +107,11 @@ latent_attn_generic_kernel(const T* __restrict__ ql, long long ql_row, long long
 #pragma unroll
   for (int i = 0; i < ND; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
-  for (int kb = 0; kb <= hi; kb += 32) {
+  // a window keeps the keys hi - window + 1 .. hi; pages before it may have been given back and are never touched
+  const int lo = window > 0 ? max(0, hi - window + 1) : 0;
+  for (int kb = lo & ~31; kb <= hi; kb += 32) {
     const int key = kb + lane;
-    bool valid = key <= hi;
+    bool valid = key <= hi && key >= lo;
     long long koff = 0;
     float s = -INFINITY;
     if (valid && !bspec::in_range(table[key / page_size], n_pages, 111)) valid = false;
@@ -139,6 +142,14 @@ latent_attn_generic_kernel(const T* __restrict__ ql, long long ql_row, long long
       }
     }
     m = m_new;
+  }
+  if (sink != nullptr) {                          // a logit per head that joins the denominator only
+    const float sk = sink[h];
+    const float m_new = fmaxf(m, sk);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(sk - m_new);
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acc[i] *= corr;
   }
   const float inv = 1.f / l;
   T* op = out + (size_t)t * o_row + (size_t)h * o_head;
@@ -188,7 +199,8 @@ BSPEC_API int bspec_latent_attention_generic(const void* ql, long long ql_row, l
                                              long long o_head, const void* cache, int dtype, const int* qo_indptr,
                                              const int* positions, const int* kv_indptr, const int* kv_indices,
                                              int n_entries, int max_q_len, int H, int R, int P, int page_size,
-                                             float scale, long long n_pages, cudaStream_t stream) {
+                                             float scale, long long n_pages, int window, const float* sink,
+                                             cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return 0;
   if (R <= 0 || R > 1024 || P < 0) return (int)cudaErrorInvalidValue;
   dim3 grid((max_q_len + GW - 1) / GW, n_entries, H);
@@ -197,7 +209,8 @@ BSPEC_API int bspec_latent_attention_generic(const void* ql, long long ql_row, l
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
 #define LG(T, ND) BSPEC_LAUNCH((latent_attn_generic_kernel<T, ND>), grid, GW * 32, smem, stream, (const T*)ql, ql_row, \
                                ql_head, (const T*)qr, qr_row, qr_head, (T*)out, o_row, o_head, (const T*)cache,       \
-                               qo_indptr, positions, kv_indptr, kv_indices, H, R, P, page_size, scale, n_pages)
+                               qo_indptr, positions, kv_indptr, kv_indices, H, R, P, page_size, scale, n_pages,   \
+                               window, sink)
   const int nd = (R + 31) / 32;
   if (dtype == BSPEC_F32) {
     if (nd <= 4) LG(float, 4); else if (nd <= 8) LG(float, 8); else if (nd <= 16) LG(float, 16); else LG(float, 32);

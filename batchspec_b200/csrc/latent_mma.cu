@@ -72,7 +72,8 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
                        const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                        const int* __restrict__ kv_indices, int H, int R, int P, int page_size, float scale,
                        int n_splits, float* __restrict__ o_part, float* __restrict__ ml_part, long long n_pages,
-                       const float* __restrict__ inv_freq, float magnitude) {
+                       const float* __restrict__ inv_freq, float magnitude, int window,
+                       const float* __restrict__ sink) {
   constexpr int BM = 16 * RG;
   constexpr int KW = BN / CH;                     // keys of a score tile per warp: 16 or 8
   constexpr int TPR = 2 * CH, KPT = BN / TPR;     // softmax: threads per row, keys per thread
@@ -99,9 +100,13 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   const int pos0 = positions[q_begin];
   const int last_tok = (int)min((long long)q_len - 1, (row0 + BM - 1) / H);
   const int max_pos = pos0 + last_tok;
+  // with a window the CTA's first row sees nothing before min_key: the tiles start there, and entries before it
+  // (their pages may have been given back) are never looked up
+  const int min_key = window > 0 ? max(0, pos0 + (int)(row0 / H) - window + 1) : 0;
+  const int tile0 = min_key / BN;
   const int n_tiles = max_pos / BN + 1;
-  const int per = (n_tiles + n_splits - 1) / n_splits;
-  const int t_begin = split * per, t_end = min(n_tiles, t_begin + per);
+  const int per = (n_tiles - tile0 + n_splits - 1) / n_splits;
+  const int t_begin = tile0 + split * per, t_end = min(n_tiles, t_begin + per);
   const int* table = kv_indices + kv_indptr[e];
 
   // ---- queries: row r holds [ql | qr] of (token, head) = divmod(row0 + r, H); rows past the portion are zero.
@@ -156,7 +161,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
     long long off = -1;
     if (lane < KPW && tile < t_end) {
       const int key = tile * BN + warp + lane * NW;
-      if (key <= max_pos) {
+      if (key <= max_pos && key >= min_key) {
         const int slot = ps_shift >= 0 ? key >> ps_shift : key / page_size;
         const int page = table[slot];
         if (bspec::in_range(page, n_pages, 112)) off = ((long long)page * page_size + (key - slot * page_size)) * D;
@@ -199,11 +204,12 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   const uint32_t pl_s = smem_addr(Pl + (size_t)(16 * rg + 8 * (mat & 1) + r8) * PP + 8 * (mat >> 1));
   const uint32_t vt_s = smem_addr(Ks + (size_t)(8 * (mat & 1) + r8) * DP + col0 + 8 * (mat >> 1));
   // the last key each of this thread's two score rows may see (-1: the row is past the portion)
-  int row_pos[2];
+  int row_pos[2], row_lo[2];
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const long long row = row0 + 16 * rg + qrow + 8 * half;
     row_pos[half] = row < rows_total ? pos0 + (int)(row / H) : -1;
+    row_lo[half] = window > 0 ? row_pos[half] - window + 1 : 0;         // the first key the row sees
   }
 
   long long ahead = lookup(t_begin);
@@ -278,8 +284,10 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
           const int c = KW * ch + 8 * nt + qcol;
           const int key = tile * BN + c;
           float2 v;
-          v.x = key <= row_pos[half] ? (s[0][nt][2 * half] + s[2][nt][2 * half]) * scale : -INFINITY;
-          v.y = key + 1 <= row_pos[half] ? (s[0][nt][2 * half + 1] + s[2][nt][2 * half + 1]) * scale : -INFINITY;
+          v.x = (key <= row_pos[half] && key >= row_lo[half])
+                    ? (s[0][nt][2 * half] + s[2][nt][2 * half]) * scale : -INFINITY;
+          v.y = (key + 1 <= row_pos[half] && key + 1 >= row_lo[half])
+                    ? (s[0][nt][2 * half + 1] + s[2][nt][2 * half + 1]) * scale : -INFINITY;
           *reinterpret_cast<float2*>(Ss + r * SP + c) = v;
         }
     }
@@ -365,6 +373,28 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   }
   cp_async_wait<0>();
   __syncthreads();          // row_m / row_l of the init (no tiles) or of the last tile, for every warp
+  // The sink: a logit per head whose exponential joins the denominator.  The first share takes it, as one more
+  // (valueless) key: its maximum, sum and output are rescaled the way a tile rescales them.
+  if (sink != nullptr && split == 0) {
+    if (tid < BM) {
+      const long long row = row0 + tid;
+      float corr = 1.f;
+      if (row < rows_total) {
+        const float sk = sink[(int)(row % H)];
+        const float m_old = row_m[tid], m_new = fmaxf(m_old, sk);
+        corr = m_old == -INFINITY ? 0.f : __expf(m_old - m_new);
+        row_m[tid] = m_new;
+        row_l[tid] = row_l[tid] * corr + __expf(sk - m_new);
+      }
+      row_c[tid] = corr;
+    }
+    __syncthreads();
+    const float c_lo = row_c[16 * rg + qrow], c_hi = row_c[16 * rg + qrow + 8];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi;
+    }
+  }
 
   // ---- results
 #pragma unroll
@@ -491,8 +521,8 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
                                          const int* positions, const int* kv_indptr, const int* kv_indices,
                                          int n_entries, int n_tokens, int max_q_len, int H, int R, int P,
                                          int page_size, float scale, int n_splits, float* o_part, float* ml_part,
-                                         long long n_pages, const float* inv_freq, float magnitude,
-                                         cudaStream_t stream) {
+                                         long long n_pages, const float* inv_freq, float magnitude, int window,
+                                         const float* sink, cudaStream_t stream) {
   const bool wide = prompt_mode() != 1;
   if (n_entries <= 0 || max_q_len <= 0) return 0;
   if (!bspec_latent_attention_mma_supported(R, P) || n_splits < 1 || (n_splits > 1 && (!o_part || !ml_part)))
@@ -510,7 +540,7 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
     BSPEC_LAUNCH((latent_attn_mma_kernel<RG, CH, N>), grid, 32 * RG * CH, smem, stream, (const __nv_bfloat16*)ql,    \
                  ql_row, ql_head, (const __nv_bfloat16*)qr, qr_row, qr_head, (__nv_bfloat16*)out, o_row, o_head,     \
                  (const __nv_bfloat16*)cache, qo_indptr, positions, kv_indptr, kv_indices, H, R, P, page_size,       \
-                 scale, n_splits, o_part, ml_part, n_pages, inv_freq, magnitude);                                    \
+                 scale, n_splits, o_part, ml_part, n_pages, inv_freq, magnitude, window, sink); \
   } while (0)
 #define LM1(RG, CH, N)                                                                                               \
   do {                                                                                                               \
@@ -518,7 +548,7 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
     BSPEC_LAUNCH((latent_attn_mma_kernel<RG, CH, N, 1>), grid, 32 * RG * CH, smem, stream, (const __nv_bfloat16*)ql, \
                  ql_row, ql_head, (const __nv_bfloat16*)qr, qr_row, qr_head, (__nv_bfloat16*)out, o_row, o_head,     \
                  (const __nv_bfloat16*)cache, qo_indptr, positions, kv_indptr, kv_indices, H, R, P, page_size,       \
-                 scale, n_splits, o_part, ml_part, n_pages, inv_freq, magnitude);                                    \
+                 scale, n_splits, o_part, ml_part, n_pages, inv_freq, magnitude, window, sink); \
   } while (0)
   if (small_pair) {
     const int ntw = R / 32;

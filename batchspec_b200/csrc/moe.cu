@@ -4,7 +4,9 @@
 //   route     per token: z = Wr h in float32, s = sigmoid(z), choice = s + correction; the experts come in equal
 //             groups of neighbours, a group's score is the sum of its two largest choices, only the best `keep`
 //             groups stay (the others count as minus infinity); the `top` largest choices are taken, ties to the
-//             lower index; weights = s of the chosen * scale (no renormalisation)
+//             lower index; weights = s of the chosen * scale (no renormalisation).  With `softmax_top` instead:
+//             choice = z + bias (the `correction` tensor), the `top` largest are taken, and the weights are the
+//             softmax over the chosen logits alone
 //   plan      one block: counts per expert, a stable counting sort of the n*top slots by expert (row r of the
 //             sorted order holds slot perm[r]; inv[slot] = r), and the list of row tiles (expert, first row, rows)
 //   grouped   C[r, :] = act(A[src(r), :] . W[expert(r)]^T) over the tiles of the plan; every output element is one
@@ -26,7 +28,7 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ h, int d, const T* __restrict__ wr, const void* __restrict__ corr,
                  int corr_dtype, int E, int G, int keep, int top, float scale, int* __restrict__ ids,
-                 float* __restrict__ wts, const float* __restrict__ logits) {
+                 float* __restrict__ wts, const float* __restrict__ logits, int softmax_top) {
   bspec::pdl_prologue(50);
   extern __shared__ float sm[];
   float* hs = sm;                 // [d]
@@ -35,9 +37,10 @@ moe_route_kernel(const T* __restrict__ h, int d, const T* __restrict__ wr, const
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (logits != nullptr) {            // the logits were formed by a matrix product (many tokens)
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
-      const float s = 1.f / (1.f + expf(-logits[(size_t)t * E + e]));
+      const float z = logits[(size_t)t * E + e], b = corr != nullptr ? load_as_f32(corr, corr_dtype, e) : 0.f;
+      const float s = softmax_top ? z + b : 1.f / (1.f + expf(-z));
       sc[e] = s;
-      ch[e] = s + (corr != nullptr ? load_as_f32(corr, corr_dtype, e) : 0.f);
+      ch[e] = softmax_top ? s : s + b;
     }
   } else {
     for (int i = threadIdx.x; i < d; i += blockDim.x) hs[i] = to_f32(h[(size_t)t * d + i]);
@@ -48,9 +51,10 @@ moe_route_kernel(const T* __restrict__ h, int d, const T* __restrict__ wr, const
       for (int i = lane; i < d; i += 32) z += hs[i] * to_f32(w[i]);
       z = warp_sum(z);
       if (lane == 0) {
-        const float s = 1.f / (1.f + expf(-z));
+        const float b = corr != nullptr ? load_as_f32(corr, corr_dtype, e) : 0.f;
+        const float s = softmax_top ? z + b : 1.f / (1.f + expf(-z));
         sc[e] = s;
-        ch[e] = s + (corr != nullptr ? load_as_f32(corr, corr_dtype, e) : 0.f);
+        ch[e] = softmax_top ? s : s + b;
       }
     }
   }
@@ -102,6 +106,13 @@ moe_route_kernel(const T* __restrict__ h, int d, const T* __restrict__ wr, const
       ch[best] = NAN;                             // taken
     }
     __syncwarp();
+  }
+  if (softmax_top && lane == 0) {                 // the weights: softmax over the chosen logits alone
+    float* w = wts + (size_t)t * top;
+    float mx = -INFINITY, sum = 0.f;
+    for (int k = 0; k < top; ++k) mx = fmaxf(mx, sc[ids[(size_t)t * top + k]]);
+    for (int k = 0; k < top; ++k) sum += expf(sc[ids[(size_t)t * top + k]] - mx);
+    for (int k = 0; k < top; ++k) w[k] = expf(sc[ids[(size_t)t * top + k]] - mx) / sum * scale;
   }
 }
 
@@ -467,7 +478,7 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
 
 BSPEC_API int bspec_moe_route(const void* h, int dtype, int n, int d, const void* wr, const void* corr, int corr_dtype,
                               int E, int G, int keep, int top, float scale, int* ids, float* wts,
-                              const float* logits, cudaStream_t stream) {
+                              const float* logits, int softmax_top, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (E <= 0 || E > MAX_EXPERTS || top <= 0 || top > E || G <= 0 || E % G || keep <= 0 || keep > G ||
       (long long)keep * (E / G) < top)
@@ -477,11 +488,11 @@ BSPEC_API int bspec_moe_route(const void* h, int dtype, int n, int d, const void
   if (dtype == BSPEC_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     BSPEC_LAUNCH((moe_route_kernel<float>), n, ROUTE_THREADS, smem, stream, (const float*)h, d, (const float*)wr, corr,
-                 corr_dtype, E, G, keep, top, scale, ids, wts, logits);
+                 corr_dtype, E, G, keep, top, scale, ids, wts, logits, softmax_top);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     BSPEC_LAUNCH((moe_route_kernel<__nv_bfloat16>), n, ROUTE_THREADS, smem, stream, (const __nv_bfloat16*)h, d,
-                 (const __nv_bfloat16*)wr, corr, corr_dtype, E, G, keep, top, scale, ids, wts, logits);
+                 (const __nv_bfloat16*)wr, corr, corr_dtype, E, G, keep, top, scale, ids, wts, logits, softmax_top);
   }
   return BSPEC_LAUNCH_CHECK();
 }

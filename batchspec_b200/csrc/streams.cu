@@ -1,0 +1,160 @@
+// A residual stream kept as several copies ("streams") per token that learned coefficients mix:
+// x [n, S, d] float32.  A sublayer reads u = sum_s read[s] x_s, and its result y joins all streams at once,
+//   x_t <- sum_s mix[s, t] x_s + write[t] * (vec * y),   vec a factor per column (or none),
+// with ``mixw`` = [mix: S x S, indexed (from, to) | write: S] as one float32 table.
+//
+// Kernels:
+//   stream_expand   x[t, s, :] = src[t, :] for every s
+//   stream_norm     the pending sublayer result joins the streams (if one is given), then the next sublayer's
+//                   input is read and RMS-normalised: out = u / sqrt(mean(u^2) + eps) * w, one rounding
+//                   (the counterpart of add + RMSNorm for one stream; without ``read`` it only updates)
+//   stream_gather   out[i, :] = sum_t x'_t of row rows[i], x' the streams after the pending result has joined
+//                   (nothing is written back): the rows that go to the final norm and the head
+// All arithmetic is float32; sums over the streams run in the order of the stream index.
+#include "common.cuh"
+using namespace bspec;
+
+namespace {
+
+constexpr int MAX_STREAMS = 16;
+
+template <typename T>
+__global__ void stream_expand_kernel(const float* __restrict__ src, float* __restrict__ x, int S, int d) {
+  bspec::pdl_prologue(70);
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = src[t * d + i];
+    for (int s = 0; s < S; ++s) x[(t * S + s) * d + i] = v;
+  }
+}
+
+// The new streams of one column: old[] in, fresh[] out.
+__device__ __forceinline__ void join_column(const float* old, float y, const float* mixw, int S, float* fresh) {
+  for (int t = 0; t < S; ++t) {
+    float acc = 0.f;
+    for (int s = 0; s < S; ++s) acc += mixw[s * S + t] * old[s];
+    fresh[t] = acc + mixw[S * S + t] * y;
+  }
+}
+
+// One block per token.  u is kept in shared memory between the sum of squares and the scaling.
+template <typename TD, typename TO>
+__global__ void stream_norm_kernel(float* __restrict__ x, const TD* __restrict__ pending,
+                                   const float* __restrict__ vec, const float* __restrict__ mixw,
+                                   const float* __restrict__ read, const void* __restrict__ weight, int w_dtype,
+                                   TO* __restrict__ out, int S, int d, float eps) {
+  bspec::pdl_prologue(71);
+  extern __shared__ float u_row[];                // [d]
+  __shared__ float coef[MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS];
+  __shared__ float scratch[32];
+  const size_t t = blockIdx.x;
+  if (pending != nullptr)
+    for (int i = threadIdx.x; i < S * S + S; i += blockDim.x) coef[i] = mixw[i];
+  if (read != nullptr)
+    for (int i = threadIdx.x; i < S; i += blockDim.x) coef[MAX_STREAMS * MAX_STREAMS + MAX_STREAMS + i] = read[i];
+  __syncthreads();
+  const float* rd = coef + MAX_STREAMS * MAX_STREAMS + MAX_STREAMS;
+  float* xt = x + t * S * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float cur[MAX_STREAMS];
+    for (int s = 0; s < S; ++s) cur[s] = xt[(size_t)s * d + i];
+    if (pending != nullptr) {
+      const float y = to_f32(pending[t * d + i]) * (vec != nullptr ? vec[i] : 1.f);
+      float fresh[MAX_STREAMS];
+      join_column(cur, y, coef, S, fresh);
+      for (int s = 0; s < S; ++s) {
+        cur[s] = fresh[s];
+        xt[(size_t)s * d + i] = fresh[s];
+      }
+    }
+    if (read != nullptr) {
+      float u = 0.f;
+      for (int s = 0; s < S; ++s) u += rd[s] * cur[s];
+      u_row[i] = u;
+      ss += u * u;
+    }
+  }
+  if (read == nullptr) return;
+  const float r = 1.f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    out[t * d + i] = from_f32<TO>(u_row[i] * r * load_as_f32(weight, w_dtype, i));
+}
+
+template <typename TD>
+__global__ void stream_gather_kernel(const float* __restrict__ x, const TD* __restrict__ pending,
+                                     const float* __restrict__ vec, const float* __restrict__ mixw,
+                                     const int* __restrict__ rows, float* __restrict__ out, int S, int d, int n_src) {
+  bspec::pdl_prologue(72);
+  __shared__ float coef[MAX_STREAMS * MAX_STREAMS + MAX_STREAMS];
+  if (!bspec::in_range(rows[blockIdx.x], n_src, 102)) return;
+  if (pending != nullptr)
+    for (int i = threadIdx.x; i < S * S + S; i += blockDim.x) coef[i] = mixw[i];
+  __syncthreads();
+  const size_t t = rows[blockIdx.x];
+  const float* xt = x + t * S * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float cur[MAX_STREAMS];
+    for (int s = 0; s < S; ++s) cur[s] = xt[(size_t)s * d + i];
+    if (pending != nullptr) {
+      const float y = to_f32(pending[t * d + i]) * (vec != nullptr ? vec[i] : 1.f);
+      float fresh[MAX_STREAMS];
+      join_column(cur, y, coef, S, fresh);
+      for (int s = 0; s < S; ++s) cur[s] = fresh[s];
+    }
+    float sum = 0.f;
+    for (int s = 0; s < S; ++s) sum += cur[s];
+    out[(size_t)blockIdx.x * d + i] = sum;
+  }
+}
+
+}  // namespace
+
+BSPEC_API int bspec_stream_expand(const float* src, float* x, int n, int S, int d, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (S <= 0 || S > MAX_STREAMS) return (int)cudaErrorInvalidValue;
+  BSPEC_LAUNCH((stream_expand_kernel<float>), n, d >= 1024 ? 256 : 128, 0, stream, src, x, S, d);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// pending null: nothing joins.  read null: the streams are only updated (weight and out unused).
+BSPEC_API int bspec_stream_norm(float* x, const void* pending, int pending_dtype, const float* vec, const float* mixw,
+                                const float* read, const void* weight, int w_dtype, void* out, int out_dtype, int n,
+                                int S, int d, float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (S <= 0 || S > MAX_STREAMS || (pending != nullptr && mixw == nullptr) || (read != nullptr && (!weight || !out)))
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+#define LN(TD, TO)                                                                                                  \
+  do {                                                                                                              \
+    if (smem > 48 * 1024)                                                                                           \
+      cudaFuncSetAttribute(stream_norm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    BSPEC_LAUNCH((stream_norm_kernel<TD, TO>), n, threads, smem, stream, x, (const TD*)pending, vec, mixw, read,    \
+                 weight, w_dtype, (TO*)out, S, d, eps);                                                             \
+  } while (0)
+  if (pending_dtype == BSPEC_F32 && out_dtype == BSPEC_F32) LN(float, float);
+  else if (pending_dtype == BSPEC_BF16 && out_dtype == BSPEC_BF16) LN(__nv_bfloat16, __nv_bfloat16);
+  else if (pending_dtype == BSPEC_F32 && out_dtype == BSPEC_BF16) LN(float, __nv_bfloat16);
+  else LN(__nv_bfloat16, float);
+#undef LN
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_stream_gather(const float* x, const void* pending, int pending_dtype, const float* vec,
+                                  const float* mixw, const int* rows, float* out, int n_out, int S, int d, int n_src,
+                                  cudaStream_t stream) {
+  if (n_out <= 0) return 0;
+  if (S <= 0 || S > MAX_STREAMS || (pending != nullptr && mixw == nullptr)) return (int)cudaErrorInvalidValue;
+  if (pending_dtype == BSPEC_F32)
+    BSPEC_LAUNCH((stream_gather_kernel<float>), n_out, 256, 0, stream, x, (const float*)pending, vec, mixw, rows, out,
+                 S, d, n_src);
+  else
+    BSPEC_LAUNCH((stream_gather_kernel<__nv_bfloat16>), n_out, 256, 0, stream, x, (const __nv_bfloat16*)pending, vec,
+                 mixw, rows, out, S, d, n_src);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_streams)
+BSPEC_DEFINE_BOUNDS_REPORT(bspec_bounds_report_streams)

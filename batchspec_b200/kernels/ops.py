@@ -61,10 +61,10 @@ _SIGNATURES = {
     "bspec_relu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_qkv_prepare": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float,
                           c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                          c_longlong, c_void_p],
+                          c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "bspec_attention_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
-                               c_longlong, c_float, c_int, c_void_p, c_longlong, c_longlong, c_float, c_void_p],
+                               c_longlong, c_float, c_int, c_void_p, c_longlong, c_longlong, c_float, c_int, c_void_p],
     "bspec_delta_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                             c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                             c_int, c_int, c_int, c_float, c_float, c_void_p],
@@ -80,23 +80,30 @@ _SIGNATURES = {
                             c_void_p],
     "bspec_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "bspec_gelu_erf": [c_void_p, c_int, c_longlong, c_void_p],
+    "bspec_relu_squared": [c_void_p, c_int, c_longlong, c_void_p],
+    "bspec_stream_expand": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "bspec_stream_norm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                          c_int, c_int, c_float, c_void_p],
+    "bspec_stream_gather": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                            c_void_p],
     "bspec_tanh_softcap": [c_void_p, c_longlong, c_float, c_void_p],
     "bspec_latent_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
                              c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_longlong, c_void_p],
     "bspec_latent_attention_generic": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p,
                                        c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p],
+                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_int, c_void_p,
+                                       c_void_p],
     "bspec_latent_attention_mma_supported": [c_int, c_int],
     "bspec_latent_attention_mma_rows": [c_int, c_int, c_int, c_int],
     "bspec_latent_attention_mma_smem": [c_int, c_int, c_int, c_int],
     "bspec_latent_attention_mma": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p,
                                    c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong,
-                                   c_void_p, c_float, c_void_p],
+                                   c_void_p, c_float, c_int, c_void_p, c_void_p],
     "bspec_gate_heads": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                        c_void_p, c_void_p, c_void_p, c_void_p],
+                        c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "bspec_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                        c_void_p, c_void_p],
     "bspec_moe_grouped": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
@@ -201,13 +208,13 @@ def set_pdl(on: bool) -> None:
 _TRACE_SETTERS = ["bspec_trace_set_attention_tcgen05", "bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
                   "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05", "bspec_trace_set_latent",
                   "bspec_trace_set_moe", "bspec_trace_set_latent_mma", "bspec_trace_set_delta",
-                  "bspec_trace_set_state_mixers"]
+                  "bspec_trace_set_state_mixers", "bspec_trace_set_streams"]
 TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "silu_mul", 5: "rope_kv_append",
                       6: "rope_inplace", 7: "attn_generic", 8: "attn_decode", 9: "attn_prefill", 10: "sgemm",
                       11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 14: "add_layernorm", 15: "clamped_glu",
                       16: "gelu_erf", 17: "tanh_softcap", 18: "residual_update", 19: "qkv_prepare", 60: "delta_prepare",
                       61: "delta_recurrence", 62: "gated_rmsnorm", 63: "bigram_add", 64: "scale", 65: "lightning_recurrence",
-                      66: "scan_conv", 67: "selective_scan", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
+                      66: "scan_conv", 67: "selective_scan", 70: "stream_expand", 71: "stream_norm", 72: "stream_gather", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
                       41: "latent_attn_generic", 42: "gate_heads", 43: "latent_attn_mma", 44: "latent_attn_join",
                       50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine", 55: "moe_skinny", 56: "moe_skinny_mma", 57: "moe_rank", 58: "moe_offsets", 59: "moe_place"}
 
@@ -377,6 +384,69 @@ def gelu_erf_(x: torch.Tensor) -> torch.Tensor:
     assert x.is_contiguous()
     _check(load_library().bspec_gelu_erf(x.data_ptr(), _dtype_code(x.dtype), x.numel(), _stream()), "gelu_erf")
     return x
+
+
+def relu_squared_(x: torch.Tensor) -> torch.Tensor:
+    """In place max(x, 0)^2, float32 arithmetic."""
+    _require_cuda(x)
+    assert x.is_contiguous()
+    _check(load_library().bspec_relu_squared(x.data_ptr(), _dtype_code(x.dtype), x.numel(), _stream()), "relu_squared")
+    return x
+
+
+# ---------------------------------------------------------------------------- several residual streams
+
+def _stream_args(x, pending, vec, mixw):
+    n, S, d = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    if pending is not None:
+        assert pending.shape == (n, d) and pending.is_contiguous()
+        assert mixw is not None and mixw.dtype == torch.float32 and mixw.numel() == S * S + S and mixw.is_contiguous()
+        assert vec is None or (vec.dtype == torch.float32 and vec.numel() == d and vec.is_contiguous())
+    return n, S, d
+
+
+def stream_expand(src: torch.Tensor, streams: int) -> torch.Tensor:
+    """[n, d] float32 -> [n, streams, d]: every stream starts as the same row."""
+    require("streams")
+    _require_cuda(src)
+    assert src.dtype == torch.float32 and src.is_contiguous()
+    n, d = src.shape
+    x = torch.empty((n, streams, d), dtype=torch.float32, device=src.device)
+    _check(load_library().bspec_stream_expand(src.data_ptr(), x.data_ptr(), n, streams, d, _stream()), "stream_expand")
+    return x
+
+
+def stream_norm(x: torch.Tensor, pending: Optional[torch.Tensor], vec: Optional[torch.Tensor],
+                mixw: Optional[torch.Tensor], read: Optional[torch.Tensor], weight: Optional[torch.Tensor] = None,
+                eps: float = 0.0, out: Optional[torch.Tensor] = None) -> None:
+    """x [n, S, d] float32, in place: if ``pending`` [n, d] is given it joins all streams at once,
+    x_t <- sum_s mix[s, t] x_s + write[t] * vec * pending, ``mixw`` = [mix (S x S, from x to) | write (S)] float32 and
+    ``vec`` a float32 factor per column or None.  If ``read`` (float32 [S]) is given, out = RMS norm of
+    u = sum_s read[s] x_s times ``weight``, float32 arithmetic and one rounding."""
+    _require_cuda(x, pending, vec, mixw, read, weight, out)
+    n, S, d = _stream_args(x, pending, vec, mixw)
+    if read is not None:
+        assert read.dtype == torch.float32 and read.numel() == S and read.is_contiguous()
+        assert weight.numel() == d and out.shape == (n, d) and out.is_contiguous()
+    elif pending is None:
+        return
+    _check(load_library().bspec_stream_norm(
+        x.data_ptr(), _ptr(pending), _dtype_code(pending.dtype) if pending is not None else F32, _ptr(vec), _ptr(mixw),
+        _ptr(read), _ptr(weight), _dtype_code(weight.dtype) if weight is not None else F32, _ptr(out),
+        _dtype_code(out.dtype) if out is not None else F32, n, S, d, float(eps), _stream()), "stream_norm")
+
+
+def stream_gather(x: torch.Tensor, pending: Optional[torch.Tensor], vec: Optional[torch.Tensor],
+                  mixw: Optional[torch.Tensor], rows: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i] = the sum over the streams of row rows[i] of x [n, S, d], after ``pending`` has joined them as in
+    ``stream_norm`` (x itself is not changed)."""
+    _require_cuda(x, pending, vec, mixw, rows, out)
+    n, S, d = _stream_args(x, pending, vec, mixw)
+    assert rows.dtype == torch.int32 and out.dtype == torch.float32 and out.shape == (rows.numel(), d) and out.is_contiguous()
+    _check(load_library().bspec_stream_gather(
+        x.data_ptr(), _ptr(pending), _dtype_code(pending.dtype) if pending is not None else F32, _ptr(vec), _ptr(mixw),
+        rows.data_ptr(), out.data_ptr(), out.shape[0], S, d, n, _stream()), "stream_gather")
 
 
 GLU_FUSION = True
@@ -704,7 +774,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(qkv.dtype),
         ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
         ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, head_dim, tables.page_size, float(scale),
-        int(window), int(chunk), _ptr(sink), cache.shape[0], float(softcap), 0, None, 0, out.stride(0), 1.0, _stream()),
+        int(window), int(chunk), _ptr(sink), cache.shape[0], float(softcap), 0, None, 0, out.stride(0), 1.0, 0, _stream()),
         "attention_generic")
 
 
@@ -712,10 +782,12 @@ def qkv_prepare(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                 bias: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
                 magnitude: float, norm_eps: float, positions: torch.Tensor, tok_entry: torch.Tensor,
                 kv_indptr: torch.Tensor, kv_indices: torch.Tensor, cache: torch.Tensor, page_size: int,
-                write_kv: bool = True) -> torch.Tensor:
+                write_kv: bool = True, q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None,
+                norm_first: bool = False) -> torch.Tensor:
     """From the float32 rows [q | k | v] of the fused projection: bias, rotation of the first ``rotary_dim`` numbers
     of every q and k head (cosine and sine times ``magnitude``), division of every q and k head by its root mean
-    square (``norm_eps`` > 0), in float32; returns q [n, n_heads * head_dim] in the cache's dtype and writes k and v
+    square (``norm_eps`` > 0; times ``q_norm`` / ``k_norm``, a weight per number of a head shared by the heads, when
+    given; before the rotation with ``norm_first``, else after it), in float32; returns q [n, n_heads * head_dim] in the cache's dtype and writes k and v
     into the cache page of each token's position.  Page layout: [k: kv head, row, head_dim | v: kv head, row, v_dim].
     ``qkv`` may be a view of the leading columns of wider rows.  ``v_dim`` 0: no values (the keys serve as values)
     and a page holds keys only."""
@@ -728,37 +800,44 @@ def qkv_prepare(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
         assert bias.numel() == qkv.shape[1] and bias.is_contiguous()
     if rotary_dim:
         assert inv_freq.dtype == torch.float32 and inv_freq.shape == (2, rotary_dim // 2) and inv_freq.is_contiguous()
+    if q_norm is not None or k_norm is not None:
+        assert q_norm is not None and k_norm is not None and q_norm.dtype == k_norm.dtype and norm_eps > 0
+        assert q_norm.numel() == head_dim and k_norm.numel() == head_dim and q_norm.is_contiguous() and k_norm.is_contiguous()
     q = torch.empty((n, n_heads * head_dim), dtype=cache.dtype, device=qkv.device)
     _check(load_library().bspec_qkv_prepare(
         qkv.data_ptr(), qkv.stride(0), n, n_heads, n_kv_heads, head_dim, v_dim, _ptr(bias),
         _dtype_code(bias.dtype) if bias is not None else F32, _ptr(inv_freq), int(rotary_dim), int(bool(interleaved)),
         float(magnitude), float(norm_eps), positions.data_ptr(), tok_entry.data_ptr(), kv_indptr.data_ptr(),
         kv_indices.data_ptr(), q.data_ptr(), cache.data_ptr(), _dtype_code(cache.dtype), int(page_size),
-        int(bool(write_kv)), cache.shape[0], _stream()), "qkv_prepare")
+        int(bool(write_kv)), cache.shape[0], _ptr(q_norm), _ptr(k_norm),
+        _dtype_code(q_norm.dtype) if q_norm is not None else F32, int(bool(norm_first)), _stream()), "qkv_prepare")
     return q
 
 
 def masked_attention(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables, n_heads: int,
                      n_kv_heads: int, head_dim: int, v_dim: int, scale: float, window: int = 0, chunk: int = 0,
                      sink: Optional[torch.Tensor] = None, softcap: float = 0.0, values_are_keys: bool = False,
-                     gate: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+                     gate: Optional[torch.Tensor] = None, out_scale: float = 1.0, gate_per_head: bool = False) -> None:
     """Causal attention with optional masks and sink over pages laid out [k | v] with values of size ``v_dim``:
     ``window`` > 0 keeps the last ``window`` keys, ``chunk`` > 0 the keys of the query's own chunk of positions;
     ``sink`` (float32 per query head) adds exp(sink) to the softmax denominator; ``softcap`` c > 0 turns a scaled
     score s into c tanh(s / c); ``values_are_keys``: pages hold keys only and a key is its own value;  ``gate``
-    (a float32 view [n, n_heads * v_dim] of rows that may be wider): the output is multiplied by sigmoid(gate);
+    (a float32 view [n, n_heads * v_dim] of rows that may be wider; [n, n_heads] with ``gate_per_head``, one logit for
+    all numbers of a head): the output is multiplied by sigmoid(gate);
     ``out_scale`` multiplies it.  ``out`` may be a view of the leading columns of wider rows.  float32 arithmetic."""
     _require_cuda(q, out, cache, sink, gate)
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == q.dtype == cache.dtype
     assert out.shape == (q.shape[0], n_heads * v_dim) and (not values_are_keys or v_dim == head_dim)
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous())
-    assert gate is None or (gate.dtype == torch.float32 and gate.shape == out.shape and gate.stride(1) == 1)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and
+                            gate.shape == ((q.shape[0], n_heads) if gate_per_head else out.shape))
     _check(load_library().bspec_attention_masked(
         q.data_ptr(), q.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(q.dtype), ctx.qo_indptr.data_ptr(),
         ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(), ctx.n_entries,
         ctx.max_q_len, n_heads, n_kv_heads, head_dim, v_dim, tables.page_size, float(scale), int(window), int(chunk),
         _ptr(sink), cache.shape[0], float(softcap), int(bool(values_are_keys)), _ptr(gate),
-        gate.stride(0) if gate is not None else 0, out.stride(0), float(out_scale), _stream()), "attention_masked")
+        gate.stride(0) if gate is not None else 0, out.stride(0), float(out_scale), int(bool(gate_per_head)), _stream()),
+        "attention_masked")
 
 
 # ---------------------------------------------------------------------------- gated delta rule
@@ -947,7 +1026,8 @@ def check_status() -> None:
 
 _BOUNDS_REPORTS = ["bspec_bounds_report_state_mixers", "bspec_bounds_report_elementwise", "bspec_bounds_report_gemm_tcgen05",
                    "bspec_bounds_report_attention_generic", "bspec_bounds_report_attention_bf16",
-                   "bspec_bounds_report_latent", "bspec_bounds_report_latent_mma", "bspec_bounds_report_delta"]
+                   "bspec_bounds_report_latent", "bspec_bounds_report_latent_mma", "bspec_bounds_report_delta",
+                   "bspec_bounds_report_streams"]
 BOUNDS_CODES = {101: "token id (embedding)", 102: "row (gather)", 103: "block-table slot (rotary + cache append)",
                 104: "page id (rotary + cache append)", 105: "block-table slot (q/k/v product's epilogue)",
                 106: "page id (q/k/v product's epilogue)", 107: "page id (attention over plain loads)",
@@ -1127,13 +1207,16 @@ FORCE_GENERIC_LATENT = False       # tests set this to compare the tensor-core k
 
 
 def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables,
-                     n_heads: int, kv_rank: int, rot_dim: int, scale: float, rotate=None) -> None:
+                     n_heads: int, kv_rank: int, rot_dim: int, scale: float, rotate=None, window: int = 0,
+                     sink: Optional[torch.Tensor] = None) -> None:
     """Causal softmax attention in the latent space over the paged entries [c | kr].  ``q_lat`` [H, n, kv_rank] and
     ``q_rot`` [n, H, rot_dim] are views with a dense last dim; ``out`` [H, n, kv_rank] receives sum_j p_j c_j per
     head.  ``rotate`` None: ``q_rot`` is already rotated.  ``rotate`` = (``rope_frequency_table``, magnitude):
     it is not, and is rotated by adjacent pairs on the way, inside the tensor-core kernel as it loads the queries,
-    or in place by the rotation kernel before the generic one."""
-    _require_cuda(q_lat, q_rot, out, cache)
+    or in place by the rotation kernel before the generic one.  ``window`` > 0: a query sees its own entry and the
+    ``window - 1`` before it.  ``sink`` (float32 per head): exp(sink) joins the softmax denominator."""
+    _require_cuda(q_lat, q_rot, out, cache, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous())
     H, n, R = q_lat.shape
     assert H == n_heads and R == kv_rank and q_rot.shape == (n, H, rot_dim) and out.shape == (H, n, R)
     assert q_lat.stride(2) == 1 and q_rot.stride(2) == 1 and out.stride(2) == 1
@@ -1151,7 +1234,8 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
             # as many shares as fill the CTAs that are resident at once (one wave), at least 256 keys each
             smem = lib.bspec_latent_attention_mma_smem(rows, kv_rank, rot_dim, 0) + 1024
             slots = sm_count(q_lat.device) * max(1, min(4, (227 * 1024) // smem))
-            n_splits = max(1, min(64, slots // (ctx.n_entries * row_tiles), -(-ctx.max_kv_len // 256)))
+            keys = min(ctx.max_kv_len, window + ctx.max_q_len) if window > 0 else ctx.max_kv_len
+            n_splits = max(1, min(64, slots // (ctx.n_entries * row_tiles), -(-keys // 256)))
         o_part = ml_part = None
         if n_splits > 1:
             o_part = torch.empty((n * H * n_splits * R,), dtype=torch.float32, device=q_lat.device)
@@ -1162,7 +1246,7 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
             ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(), ctx.n_entries, n,
             ctx.max_q_len, n_heads, kv_rank, rot_dim, tables.page_size, float(scale), n_splits, _ptr(o_part),
             _ptr(ml_part), cache.shape[0], rotate[0].data_ptr() if rotate else None,
-            float(rotate[1]) if rotate else 1.0, _stream()), "latent_attention_mma")
+            float(rotate[1]) if rotate else 1.0, int(window), _ptr(sink), _stream()), "latent_attention_mma")
         if n_splits > 1:
             count_launches(1)
         return
@@ -1173,7 +1257,7 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
         out.data_ptr(), out.stride(1), out.stride(0), cache.data_ptr(), _dtype_code(cache.dtype),
         ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
         ctx.n_entries, ctx.max_q_len, n_heads, kv_rank, rot_dim, tables.page_size, float(scale), cache.shape[0],
-        _stream()), "latent_attention_generic")
+        int(window), _ptr(sink), _stream()), "latent_attention_generic")
 
 
 def latent_mma_supported(kv_rank: int, rot_dim: int) -> bool:
@@ -1202,8 +1286,10 @@ MOE_SKINNY = True                # bfloat16 steps with fewer rows per expert: th
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], n_groups: int, keep: int,
-              top: int, scale: float):
-    """(expert ids int32 [n, top], weights float32 [n, top]) of every token; the rule is in ``csrc/moe.cu``."""
+              top: int, scale: float, softmax_top: bool = False):
+    """(expert ids int32 [n, top], weights float32 [n, top]) of every token; the rule is in ``csrc/moe.cu``.
+    ``softmax_top``: the logits plus ``correction`` (a bias) choose, and the weights are the softmax over the chosen
+    logits alone; otherwise sigmoid scores."""
     _require_cuda(h, router)
     n, d = h.shape
     E = router.shape[0]
@@ -1215,32 +1301,44 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
     _check(load_library().bspec_moe_route(h.data_ptr(), _dtype_code(h.dtype), n, d, router.data_ptr(), _ptr(correction),
                                           _dtype_code(correction.dtype) if correction is not None else F32, E,
                                           int(n_groups), int(keep), int(top), float(scale), ids.data_ptr(),
-                                          wts.data_ptr(), _ptr(logits), _stream()), "moe_route")
+                                          wts.data_ptr(), _ptr(logits), int(bool(softmax_top)), _stream()), "moe_route")
     return ids, wts
 
 
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
-                out_dtype: torch.dtype) -> torch.Tensor:
+                out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
     """sum_k wts[t, k] * Wdown[e] gelu(Wup[e] h[t]) with e = ids[t, k].  ``w_up`` [E, ff, d], ``w_down`` [E, d, ff].
+    ``glu``: the experts are gated, Wdown[e] (silu(Wgate[e] h) * (Wup[e] h)), and ``w_up`` holds [gate; up] as
+    [E, 2 ff, d]; the first product then leaves its result as it is and ``silu_mul`` follows.
     The (token, choice) rows are sorted by expert on the device; no count is read on the host."""
     _require_cuda(h, ids, wts, w_up, w_down)
     lib = load_library()
     n, d = h.shape
-    E, ff, _ = w_up.shape
+    E, ff_up, _ = w_up.shape
+    ff = ff_up // 2 if glu else ff_up                 # the down projection's inner size
+    act = 0 if glu else 1                             # the first product's epilogue: 1 = gelu
     top = ids.shape[1]
     slots = n * top
-    assert w_up.shape == (E, ff, d) and w_down.shape == (E, d, ff) and w_up.is_contiguous() and w_down.is_contiguous()
+    assert w_up.shape == (E, ff_up, d) and w_down.shape == (E, d, ff) and w_up.is_contiguous() and w_down.is_contiguous()
+    assert not glu or ff_up == 2 * ff
+
+    def gated(u):
+        if not glu:
+            return u
+        m = torch.empty((slots, ff), dtype=u.dtype, device=u.device)
+        silu_mul(u, m)
+        return m
     assert h.is_contiguous() and ids.is_contiguous() and wts.is_contiguous() and h.dtype == w_up.dtype == w_down.dtype
     dev, code = h.device, _dtype_code(h.dtype)
     library = (MOE_LIBRARY_GROUPED and h.dtype == torch.bfloat16 and slots >= MOE_LIBRARY_MIN_ROWS * E
                and d % 8 == 0 and ff % 8 == 0 and hasattr(torch, "_grouped_mm"))
     # few rows per expert in bfloat16: tiles of 8 rows on the kernel that streams the experts' weights
     skinny = (not library and MOE_SKINNY and h.dtype == torch.bfloat16 and slots < 32 * E and d % 8 == 0
-              and ff % 8 == 0 and 16 * max(d, ff) <= 200 * 1024)
+              and ff % 8 == 0 and 16 * max(d, ff_up) <= 200 * 1024)
     # ... on the tensor cores when both inner sizes are multiples of 32 and 16 token rows fit shared memory
     skinny_mma = skinny and MOE_SKINNY_MMA and d % 32 == 0 and ff % 32 == 0
     # 16 token rows per tile while they leave room for three CTAs per SM and there are that many rows per expert
-    mma_rows = 16 if (32 * max(d, ff) <= 72 * 1024 and slots > 4 * E) else 8
+    mma_rows = 16 if (32 * max(d, ff_up) <= 72 * 1024 and slots > 4 * E) else 8
     BM = (mma_rows if skinny_mma else 8) if skinny else (64 if slots >= 32 * E else 16)
     max_tiles = min(slots, slots // BM + E)
     many = slots > 2048                   # the plan in three kernels over all SMs (needs counters and ranks)
@@ -1262,28 +1360,31 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
                "moe_gather")
         ends = offsets[1:]
         u = torch._grouped_mm(rows, w_up.transpose(1, 2), offs=ends)
-        gelu_erf_(u)
+        u = gated(u) if glu else gelu_erf_(u)
         y = torch._grouped_mm(u, w_down.transpose(1, 2), offs=ends)
     elif skinny_mma:
-        u = torch.empty((slots, ff), dtype=h.dtype, device=dev)
+        u = torch.empty((slots, ff_up), dtype=h.dtype, device=dev)
         y = torch.empty((slots, d), dtype=torch.float32, device=dev)
-        _check(lib.bspec_moe_skinny_mma(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, ff, d,
-                                        tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 1, mma_rows, _stream()), "moe_skinny_mma_up")
+        _check(lib.bspec_moe_skinny_mma(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, ff_up, d,
+                                        tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, act, mma_rows, _stream()), "moe_skinny_mma_up")
+        u = gated(u)
         _check(lib.bspec_moe_skinny_mma(u.data_ptr(), None, top, w_down.data_ptr(), y.data_ptr(), F32, d, ff,
                                         tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 0, mma_rows, _stream()), "moe_skinny_mma_down")
     elif skinny:
-        u = torch.empty((slots, ff), dtype=h.dtype, device=dev)
+        u = torch.empty((slots, ff_up), dtype=h.dtype, device=dev)
         y = torch.empty((slots, d), dtype=torch.float32, device=dev)
-        _check(lib.bspec_moe_skinny(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, ff, d,
-                                    tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 1, _stream()), "moe_skinny_up")
+        _check(lib.bspec_moe_skinny(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, ff_up, d,
+                                    tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, act, _stream()), "moe_skinny_up")
+        u = gated(u)
         _check(lib.bspec_moe_skinny(u.data_ptr(), None, top, w_down.data_ptr(), y.data_ptr(), F32, d, ff,
                                     tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 0, _stream()), "moe_skinny_down")
     else:
-        u = torch.empty((slots, ff), dtype=h.dtype, device=dev)
+        u = torch.empty((slots, ff_up), dtype=h.dtype, device=dev)
         y = torch.empty((slots, d), dtype=torch.float32, device=dev)
-        _check(lib.bspec_moe_grouped(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, code, ff,
-                                     d, tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, BM, 1, _stream()),
+        _check(lib.bspec_moe_grouped(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, code, ff_up,
+                                     d, tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, BM, act, _stream()),
                "moe_grouped_up")
+        u = gated(u)
         _check(lib.bspec_moe_grouped(u.data_ptr(), None, top, w_down.data_ptr(), y.data_ptr(), code, F32, d, ff,
                                      tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, BM, 0, _stream()),
                "moe_grouped_down")

@@ -10,6 +10,7 @@ from typing import Callable, Dict
 
 from ..parts.base import Runtime
 from .decoder import CacheNeed, DecoderModel, LayerCache
+from .finolix import build_finolix
 from .llama import build_llama
 from .lupusun import build_lupusun
 from .tokolorn import build_tokolorn
@@ -34,6 +35,7 @@ register_model("LlamaForCausalLM", build_llama)
 register_model("Vabanex", build_vabanex)
 register_model("Lupusun", build_lupusun)
 register_model("Tokolorn", build_tokolorn)
+register_model("Finolix", build_finolix)
 
 __all__ = ["MODEL_REGISTRY", "register_model", "get_model", "DecoderModel", "LayerCache", "CacheNeed",
-           "ModelSpec", "LayerSpec", "RunEntry", "prenorm_layer", "build_llama", "build_lupusun", "build_tokolorn", "build_vabanex"]
+           "ModelSpec", "LayerSpec", "RunEntry", "prenorm_layer", "build_finolix", "build_llama", "build_lupusun", "build_tokolorn", "build_vabanex"]

@@ -146,7 +146,11 @@ class DecoderModel:
             else:
                 self.input_part.forward(resid, ctx)
         first = resid.clone() if any(run.add_input for run in s.order) else None
-        pending, scale, vec = None, 1.0, None
+        if s.streams:
+            if first is not None:
+                raise ValueError("a model of several residual streams cannot add its input again before a run")
+            resid = ops.stream_expand(resid, s.streams)           # [n, S, d]
+        pending, scale, vec, mix = None, 1.0, None, None
         for e, run in enumerate(s.order):
             if run.add_input:
                 ops.residual_update(resid, pending, scale, first, vec)
@@ -157,17 +161,30 @@ class DecoderModel:
             extra = {} if scale == 1.0 else {"pending_scale": scale}
             if vec is not None:
                 extra["pending_vec"] = vec
+            if mix is not None:
+                extra["pending_mix"] = mix
             resid, pending = block.forward(resid, pending, ctx, self.caches[e], **extra)
             scale, vec = getattr(block, "residual_mult", 1.0), getattr(block, "residual_vec", None)
+            mix = getattr(block, "residual_mix", None)
+            if s.streams and (mix is None or scale != 1.0):
+                raise ValueError(f"block kind {block.kind!r} does not keep several residual streams")
             if self.layer_probe is not None:
-                after = resid.clone()
-                ops.residual_update(after, pending, scale, vec=vec)
+                if s.streams:
+                    after = torch.empty((n, s.hidden_size), dtype=torch.float32, device=self.runtime.device)
+                    every = torch.arange(n, dtype=torch.int32, device=self.runtime.device)
+                    ops.stream_gather(resid, pending, vec, mix, every, after)
+                else:
+                    after = resid.clone()
+                    ops.residual_update(after, pending, scale, vec=vec)
                 self.layer_probe(e, after)
         n_out = ctx.n_logit_rows
         if n_out == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.runtime.device)
         picked = torch.empty((n_out, s.hidden_size), dtype=torch.float32, device=self.runtime.device)
-        ops.gather_rows_add(resid, pending, ctx.logit_rows, picked, scale, vec)
+        if s.streams:
+            ops.stream_gather(resid, pending, vec, mix, ctx.logit_rows, picked)
+        else:
+            ops.gather_rows_add(resid, pending, ctx.logit_rows, picked, scale, vec)
         z = self.final_norm.forward(picked, None)
         with bucket("lm_head"):
             logits = ops.linear(z, self.head, out_dtype=torch.float32)

@@ -59,3 +59,7 @@ class ModelSpec:
     input_names: Dict[str, str] = field(default_factory=dict)
     logits_part: Optional[PartSpec] = None
     logits_names: Dict[str, str] = field(default_factory=dict)
+    # 0: one residual stream [n, d].  S > 0: the residual is kept as S streams per token [n, S, d] that all start as
+    # the embedding (after the input part); the blocks' kinds must be ones that take such a residual, and the sum
+    # of the streams goes to the final norm
+    streams: int = 0

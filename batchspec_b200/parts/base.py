@@ -9,7 +9,7 @@ checkpoint names.  The reference fixes the parts by subclass hooks
 one model may mix different mixers and feed-forwards.
 
 Registries: ``MIXERS``, ``FEED_FORWARDS``, ``NORMS``, ``POSITION_ENCODINGS``,
-``BLOCKS``, ``BRANCH_SCALES``, ``INPUT_PARTS``, ``LOGITS_PARTS``.  ``register_part(registry, kind)``
+``BLOCKS``, ``BRANCH_SCALES``, ``STREAM_MIXES``, ``INPUT_PARTS``, ``LOGITS_PARTS``.  ``register_part(registry, kind)``
 is a class decorator; ``build_part(registry, spec, runtime)`` instantiates
 ``spec.kind`` with ``spec.params``.
 """
@@ -176,6 +176,7 @@ NORMS: Dict[str, type] = {}
 POSITION_ENCODINGS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
 BRANCH_SCALES: Dict[str, type] = {}
+STREAM_MIXES: Dict[str, type] = {}
 INPUT_PARTS: Dict[str, type] = {}
 LOGITS_PARTS: Dict[str, type] = {}
 
@@ -194,11 +195,15 @@ class Block:
     residual and its own last branch output, so the add can be fused into the next norm.  ``residual_mult``
     is the factor of the branch a block returns; a block that also multiplies that branch by a learned factor per
     column has it (float32 [d]) in ``residual_vec``, and whoever adds the branch applies both (the next block gets
-    the vector as ``pending_vec``)."""
+    the vector as ``pending_vec``).  A block of a model that keeps several residual streams per token gets them as
+    ``resid`` [n, S, d]; the coefficients with which its last branch joins the streams are its ``residual_mix``
+    (float32 [S * S + S]: the mix matrix indexed (from, to), then the factor of the branch per stream), handed on as
+    ``pending_mix``."""
     SLOTS: Dict[str, Dict[str, type]] = {}
     MIXER_SLOT = "mixer"
     residual_mult = 1.0
     residual_vec = None
+    residual_mix = None
 
     def __init__(self, **parts):
         missing, extra = set(self.SLOTS) - set(parts), set(parts) - set(self.SLOTS)

@@ -8,6 +8,10 @@ With h a token's normed input, H heads, per head ``dim`` unrotated and ``rot_dim
     k_h = Wuk_h c,  v_h = Wuv_h c             score_h(i, j) = (q_h . k_h(j) + rot(qr_h, i) . rot(kr, j)) * scale
     out = Wo concat_h(sigmoid(Wg h)_h * sum_j softmax_j(score_h(i, .)) v_h(j))
 
+Options: ``gated`` False leaves the gate out; ``window`` W keeps the keys i - W + 1 .. i of query i (pages that the
+window has passed are given back); ``sink``: a learned logit per head whose exponential joins the softmax
+denominator, with no key and no value.
+
 Only [c | rot(kr)] is cached (one tensor per token, ``kv_rank + rot_dim`` numbers).  The per-head keys and values
 are never formed: since q_h . (Wuk_h c) = (Wuk_h^T q_h) . c, the unrotated query is taken into the latent space
 (one small product per head), attention runs there for all heads over the same entries, and the head's value
@@ -33,11 +37,16 @@ class LatentAttention(Mixer):
     graph_safe = True
 
     def __init__(self, runtime: Runtime, dim: int, n_heads: int, head_dim: int, rot_dim: int, v_dim: int, q_rank: int,
-                 kv_rank: int, scale: float, eps: float, position: PartSpec, gated: bool = True):
+                 kv_rank: int, scale: float, eps: float, position: PartSpec, gated: bool = True, window: int = 0,
+                 sink: bool = False):
         self.runtime = runtime
         self.dim, self.n_heads, self.head_dim, self.rot_dim = int(dim), int(n_heads), int(head_dim), int(rot_dim)
         self.v_dim, self.q_rank, self.kv_rank = int(v_dim), int(q_rank), int(kv_rank)
         self.scale, self.eps, self.gated = float(scale), float(eps), bool(gated)
+        self.window, self.sink = int(window or 0), bool(sink)
+        if self.window < 0:
+            raise ValueError(f"a sliding window is positive, got {window}")
+        self.sinks = None
         if self.rot_dim % 2 or self.rot_dim <= 0:
             raise ValueError(f"the rotated part of a head must have an even, positive size, got {rot_dim}")
         if min(self.n_heads, self.head_dim, self.v_dim, self.q_rank, self.kv_rank) <= 0:
@@ -58,6 +67,8 @@ class LatentAttention(Mixer):
                  "o": ParamSpec((self.dim, H * self.v_dim))}
         if self.gated:
             specs["g"] = ParamSpec((H, self.dim))
+        if self.sink:
+            specs["sink"] = ParamSpec((H,), role="vector")
         return specs
 
     def bind(self, params):
@@ -74,8 +85,14 @@ class LatentAttention(Mixer):
         self.n_q, self.n_kv = params["dq_norm"], params["dkv_norm"]
         if self.n_kv.dtype != self.n_q.dtype:
             self.n_kv = self.n_kv.to(self.n_q.dtype)
+        if self.sink:
+            self.sinks = params["sink"].to(torch.float32).contiguous()
+        if not self.gated:
+            self.open_gate = torch.full((1, H), 1e4, dtype=torch.float32, device=self.w_o.device)   # sigmoid -> 1
 
     def cache_spec(self) -> CacheSpec:
+        if self.window:
+            return CacheSpec("window", (self.kv_rank + self.rot_dim,), self.window, tensors=1)
         return CacheSpec("full", (self.kv_rank + self.rot_dim,), tensors=1)
 
     def forward(self, x, ctx, cache):
@@ -97,7 +114,7 @@ class LatentAttention(Mixer):
         o_lat = torch.empty((H, n, R), dtype=x.dtype, device=x.device)
         with bucket("attn.compute"):
             ops.latent_attention(q_lat, q_rot, o_lat, cache.kv, ctx, tables, H, R, P, self.scale,
-                                 rotate=(pos.inv_freq, pos.magnitude))
+                                 rotate=(pos.inv_freq, pos.magnitude), window=self.window, sink=self.sinks)
         with bucket("attn.v_proj"):
             v = ops.linear_batched(o_lat, self.w_uv)                                        # [H, n, v_dim]
         heads = torch.empty((n, H * self.v_dim), dtype=x.dtype, device=x.device)
@@ -105,7 +122,7 @@ class LatentAttention(Mixer):
             if self.gated:
                 gate = down[:, self.q_rank + R + P:self.q_rank + R + P + H]
             else:
-                gate = torch.full((n, H), 1e4, dtype=torch.float32, device=x.device)        # sigmoid -> 1
+                gate = self.open_gate.expand(n, H)                  # every row reads the same logits (row stride 0)
             ops.gate_heads(v, gate, heads)
         with bucket("attn.o_proj"):
             return ops.linear(heads, self.w_o)

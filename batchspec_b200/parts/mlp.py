@@ -94,3 +94,32 @@ class ClampedGLU(FeedForward):
                 ops.clamped_glu(u, m, self.alpha, self.limit)
         with bucket("mlp.down_proj"):
             return ops.linear(m, self.w2)
+
+
+@register_part(FEED_FORWARDS, "mlp")
+class PlainMLP(FeedForward):
+    """Two matrices and an activation between them: out = Wdown act(Wup x), no gate and no biases.
+    ``activation``: "relu2" (the square of relu) or "gelu" (the exact one)."""
+    graph_safe = True
+    ACTIVATIONS = {"relu2": ops.relu_squared_, "gelu": ops.gelu_erf_}
+
+    def __init__(self, runtime: Runtime, dim: int, intermediate: int, activation: str = "relu2"):
+        self.runtime, self.dim, self.intermediate = runtime, int(dim), int(intermediate)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"feed-forward activation {activation!r} is not known ({sorted(self.ACTIVATIONS)})")
+        self.activation = activation
+        self.w1 = self.w2 = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"up": ParamSpec((self.intermediate, self.dim)), "down": ParamSpec((self.dim, self.intermediate))}
+
+    def bind(self, params):
+        self.w1, self.w2 = params["up"].contiguous(), params["down"].contiguous()
+
+    def forward(self, x, ctx):
+        with bucket("mlp.up_proj"):
+            u = ops.linear(x, self.w1)
+        with bucket("mlp.act"):
+            self.ACTIVATIONS[self.activation](u)
+        with bucket("mlp.down_proj"):
+            return ops.linear(u, self.w2)

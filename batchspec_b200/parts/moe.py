@@ -56,3 +56,43 @@ class RoutedGelu(FeedForward):
                                      self.scale)
         with bucket("mlp.experts"):
             return ops.moe_experts(x, ids, wts, self.w_up, self.w_down, x.dtype)
+
+
+@register_part(FEED_FORWARDS, "routed_glu")
+class RoutedGLU(FeedForward):
+    """Routed gated experts with a softmax over the chosen logits: z = Wr h + b in float32; the ``top`` experts of
+    largest z are taken and weighted by the softmax over those ``top`` logits alone; expert e is
+    Wdown_e (silu(Wgate_e h) * (Wup_e h)), no biases; the output is the weighted sum.  [gate; up] of every expert is
+    one stacked matrix, so the first grouped product gives both halves."""
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, dim: int, intermediate: int, n_experts: int, top: int, bias: bool = True):
+        self.runtime, self.dim, self.intermediate = runtime, int(dim), int(intermediate)
+        self.n_experts, self.top, self.bias = int(n_experts), int(top), bool(bias)
+        if not 0 < self.top <= self.n_experts:
+            raise ValueError(f"cannot choose {top} of {n_experts} experts")
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = {"router": ParamSpec((self.n_experts, self.dim))}
+        if self.bias:
+            specs["router_bias"] = ParamSpec((self.n_experts,), role="vector")
+        for e in range(self.n_experts):
+            specs[f"gate{e}"] = ParamSpec((self.intermediate, self.dim))
+            specs[f"up{e}"] = ParamSpec((self.intermediate, self.dim))
+            specs[f"down{e}"] = ParamSpec((self.dim, self.intermediate))
+        return specs
+
+    def bind(self, params):
+        if torch.device(self.runtime.device).type == "cuda":
+            ops.require("moe")                    # the kernels of csrc/moe.cu
+        self.w_router = params["router"].contiguous()
+        self.b_router = params["router_bias"].contiguous() if self.bias else None
+        self.w_up = torch.stack([torch.cat([params[f"gate{e}"], params[f"up{e}"]], dim=0)
+                                 for e in range(self.n_experts)]).contiguous()               # [E, 2 ff, d]
+        self.w_down = torch.stack([params[f"down{e}"] for e in range(self.n_experts)]).contiguous()
+
+    def forward(self, x, ctx):
+        with bucket("mlp.router"):
+            ids, wts = ops.moe_route(x, self.w_router, self.b_router, 1, 1, self.top, 1.0, softmax_top=True)
+        with bucket("mlp.experts"):
+            return ops.moe_experts(x, ids, wts, self.w_up, self.w_down, x.dtype, glu=True)

@@ -17,23 +17,42 @@ from .base import INPUT_PARTS, NORMS, InputPart, Norm, ParamSpec, Runtime, regis
 class RMSNorm(Norm):
     graph_safe = True
     def __init__(self, runtime: Runtime, dim: int, eps: float, single_rounding: bool = False,
-                 scalar_weight: bool = False):
-        """``scalar_weight``: the weight is one number (a tensor without dimensions) for all coordinates."""
+                 scalar_weight: bool = False, one_plus: bool = False):
+        """``scalar_weight``: the weight is one number (a tensor without dimensions) for all coordinates.
+        ``one_plus``: the tensor is stored around zero and the factor is 1 + w (formed once, in float32; the
+        product is then float32 with one rounding)."""
         self.runtime, self.dim, self.eps = runtime, int(dim), float(eps)
-        self.single_rounding = bool(single_rounding)
+        self.one_plus = bool(one_plus)
+        self.single_rounding = bool(single_rounding) or self.one_plus
         self.scalar_weight = bool(scalar_weight)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec(() if self.scalar_weight else (self.dim,), role="vector", init="ones_normal")}
+        return {"weight": ParamSpec(() if self.scalar_weight else (self.dim,), role="vector",
+                                    init="normal" if self.one_plus else "ones_normal")}
 
     def bind(self, params):
         self.weight = params["weight"].reshape(1).contiguous() if self.scalar_weight else params["weight"]
+        if self.one_plus:
+            self.weight = (1.0 + self.weight.to(torch.float32)).contiguous()
 
     def forward(self, resid, delta=None, delta_scale: float = 1.0, delta_vec=None):
         out = torch.empty(resid.shape, dtype=self.runtime.dtype, device=resid.device)
         with bucket("norm"):
             ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, delta_scale, self.single_rounding, delta_vec)
+        return out
+
+
+    def forward_streams(self, streams, delta=None, delta_vec=None, delta_mix=None, read=None):
+        """For a residual kept as several streams [n, S, d]: ``delta`` (times ``delta_vec`` per column) first joins
+        the streams with the coefficients ``delta_mix``; then the rows u = sum_s read[s] x_s are normalised.
+        Without ``read`` only the streams are updated."""
+        n, _, d = streams.shape
+        out = torch.empty((n, d), dtype=self.runtime.dtype, device=streams.device) if read is not None else None
+        if self.scalar_weight:
+            raise ValueError("the norm over several streams takes a weight per column")
+        with bucket("norm"):
+            ops.stream_norm(streams, delta, delta_vec, delta_mix, read, self.weight, self.eps, out)
         return out
 
 

@@ -4,6 +4,8 @@
 * values of their own size ``v_dim``;
 * a position encoding over the first numbers of each head, with a magnitude on cosine and sine (YaRN);
 * ``qk_norm_eps``: after the rotation every q and k head is divided by its root mean square (no weight);
+  ``qk_norm_weight``: the normalised head is multiplied by a learned weight per number (one for the queries, one for
+  the keys, shared by the heads); ``qk_norm_first``: the norm comes before the rotation;
 * a mask besides causality: ``chunk`` (a query sees the keys of its own chunk of ``chunk`` positions, counted from
   position 0 of the request) or ``window`` (the last ``window`` keys);
 * ``sink``: a learned logit per query head that takes part in the normalisation only:
@@ -11,7 +13,8 @@
   all heads and no tensor (0.0 adds one to the denominator);
 * ``softcap`` c: a scaled score s becomes c tanh(s / c);
 * ``values_are_keys``: there is no value projection, a key as projected is its own value, and only keys are cached;
-* ``gate``: the concatenated heads are multiplied element by element by sigmoid(Wg h) before the output projection.
+* ``gate``: the concatenated heads are multiplied element by element by sigmoid(Wg h) before the output projection;
+  ``gate="head"``: Wg has one row per head and the head's whole output is multiplied by one number.
 
 Launch sequence: one product for [Wq; Wk; Wv] with float32 output -> q/k/v preparation (bias, rotation, norms, all
 float32; q in the run dtype, k and v into their cache pages) -> attention over the pages -> output projection.
@@ -39,13 +42,18 @@ class SinkAttention(Mixer):
                  position: PartSpec, v_dim: Optional[int] = None, bias: bool = False,
                  qk_norm_eps: Optional[float] = None, chunk: Optional[int] = None, window: Optional[int] = None,
                  sink: bool = False, fixed_sink: Optional[float] = None, softcap: Optional[float] = None,
-                 values_are_keys: bool = False, gate: bool = False):
+                 values_are_keys: bool = False, gate=False, qk_norm_weight: bool = False,
+                 qk_norm_first: bool = False):
         if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
             raise ValueError(f"n_heads {n_heads} must be a positive multiple of n_kv_heads {n_kv_heads}")
         self.runtime = runtime
         self.dim, self.n_heads, self.n_kv_heads, self.head_dim = int(dim), int(n_heads), int(n_kv_heads), int(head_dim)
         self.v_dim = int(v_dim) if v_dim else self.head_dim
         self.values_are_keys, self.gate = bool(values_are_keys), bool(gate)
+        self.gate_per_head = gate == "head"
+        self.qk_norm_weight, self.qk_norm_first = bool(qk_norm_weight), bool(qk_norm_first)
+        if (self.qk_norm_weight or self.qk_norm_first) and not qk_norm_eps:
+            raise ValueError("a weight or a place for the q/k norm needs the norm itself (qk_norm_eps)")
         if self.values_are_keys and self.v_dim != self.head_dim:
             raise ValueError(f"values that are the keys have the keys' size {self.head_dim}, not {self.v_dim}")
         self.softcap = float(softcap) if softcap else 0.0
@@ -60,7 +68,7 @@ class SinkAttention(Mixer):
         if self.chunk < 0 or self.window < 0 or (self.chunk and self.window):
             raise ValueError("give a chunk size or a window, both positive, not both")
         self.position = build_part(POSITION_ENCODINGS, position, runtime)
-        self.wqkv = self.wo = self.b = self.sinks = self.sinks_l2 = None
+        self.wqkv = self.wo = self.b = self.sinks = self.sinks_l2 = self.q_norm = self.k_norm = None
         # values that are the keys, at sizes the tensor-core kernels take: those kernels read keys and values from
         # places of their own, so the key rows of the fused product are listed twice and every key is stored as its
         # own value too (twice the pages, tensor-core speed); at other sizes the pages hold keys only
@@ -73,7 +81,10 @@ class SinkAttention(Mixer):
         if self.values_are_keys:
             del specs["v"]
         if self.gate:
-            specs["g"] = ParamSpec((self.n_heads * self.v_dim, self.dim))
+            specs["g"] = ParamSpec((self.n_heads if self.gate_per_head else self.n_heads * self.v_dim, self.dim))
+        if self.qk_norm_weight:
+            specs["q_norm"] = ParamSpec((self.head_dim,), role="vector", init="ones_normal")
+            specs["k_norm"] = ParamSpec((self.head_dim,), role="vector", init="ones_normal")
         if self.bias:
             specs.update({"q_bias": ParamSpec((q,), role="vector"), "k_bias": ParamSpec((k,), role="vector"),
                           "v_bias": ParamSpec((v,), role="vector")})
@@ -82,6 +93,8 @@ class SinkAttention(Mixer):
         return specs
 
     def bind(self, params):
+        if self.gate_per_head and self._tensor_cores(self.runtime.dtype) and torch.device(self.runtime.device).type == "cuda":
+            ops.require("latent")                 # the gate per head after the tensor-core kernels (csrc/latent.cu)
         names = ("q", "k") if self.values_are_keys else ("q", "k", "v")
         if self.copy_keys:
             names = ("q", "k", "k")
@@ -91,6 +104,9 @@ class SinkAttention(Mixer):
         self.wo = params["o"].contiguous()
         if self.bias:
             self.b = torch.cat([params[n + "_bias"].to(torch.float32) for n in names]).contiguous()
+        if self.qk_norm_weight:
+            self.q_norm = params["q_norm"].contiguous()
+            self.k_norm = params["k_norm"].to(self.q_norm.dtype).contiguous()
         if self.sink:
             self.sinks = params["sink"].to(torch.float32).contiguous()
             self.sinks_l2 = ops.sink_table(self.sinks)
@@ -135,7 +151,8 @@ class SinkAttention(Mixer):
             q = ops.qkv_prepare(qkv, H, G, hd, 0 if self.values_are_keys and not self.copy_keys else vd, self.b, getattr(pos, "inv_freq", None),
                                 getattr(pos, "rotary_dim", 0), getattr(pos, "interleaved", False),
                                 getattr(pos, "magnitude", 1.0), self.qk_norm_eps, ctx.positions, ctx.tok_entry,
-                                tables.kv_indptr, tables.kv_indices, cache.kv, tables.page_size, write_kv=cache.owner)
+                                tables.kv_indptr, tables.kv_indices, cache.kv, tables.page_size, write_kv=cache.owner,
+                                q_norm=self.q_norm, k_norm=self.k_norm, norm_first=self.qk_norm_first)
         if out is None:
             out = torch.empty((n, H * vd), dtype=x.dtype, device=x.device)
         with bucket("attn.compute"):
@@ -147,10 +164,15 @@ class SinkAttention(Mixer):
                 heads = out if direct else torch.empty((n, H * vd), dtype=x.dtype, device=x.device)
                 ops.paged_attention(q, heads, cache.kv, ctx, tables, H, G, hd, self.scale, self.window, self.chunk,
                                     self.sinks, self.sinks_l2, self.softcap)
-                if not direct:
+                if not direct and self.gate_per_head and out_scale == 1.0 and out.is_contiguous():
+                    # one logit per head: the heads [n, H * vd] read as [H, n, vd]
+                    ops.gate_heads(heads.view(n, H, vd).transpose(0, 1), gate, out)
+                elif not direct:
+                    if self.gate_per_head:
+                        gate = gate.repeat_interleave(vd, dim=1)
                     ops.gate_mul(heads, gate, out, out_scale)
             else:
                 ops.masked_attention(q, out, cache.kv, ctx, tables, H, G, hd, vd, self.scale, self.window, self.chunk,
                                      self.sinks, self.softcap, self.values_are_keys and not self.copy_keys, gate,
-                                     out_scale)
+                                     out_scale, gate_per_head=self.gate_per_head)
         return out
