@@ -9,7 +9,8 @@ borrow another layer's weights; the residual may be kept as several streams.
 
 A ``latent_attention`` mixer gives heads, dim (unrotated numbers per head), rot_dim, vdim, q_rank, kv_rank, scale,
 ``rot`` {base, dims, scaling {factor, original, fast, slow} or nothing} and ``mask`` {size}: a sliding window, or
-nothing.  An ``attention`` mixer gives heads, kv_heads, dim, vdim, scale and ``rot`` {base, dims} or nothing.
+nothing.  An ``attention`` mixer gives heads, kv_heads, dim, vdim, scale, ``rot`` {base, dims} or nothing, and may
+give ``mask`` {size} too (a sliding window; without it every earlier position is seen).
 ``weights_of``: the layer has no tensors of its own and runs with layer j's, with a cache of its own.  ``streams``
 absent: one residual stream.  Every size and constant is read from here; keys this reader does not know are listed in
 ``unread_keys``."""
@@ -23,7 +24,7 @@ from .model_config import ConfigError, _take, register_config_class
 
 _TOP = {"architecture", "architectures", "vocab", "width", "norm", "streams", "layers"}
 _LATENT = {"heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "scale", "rot", "mask"}
-_ATTENTION = {"heads", "kv_heads", "dim", "vdim", "scale", "rot"}
+_ATTENTION = {"heads", "kv_heads", "dim", "vdim", "scale", "rot", "mask"}
 _SCALING = {"factor", "original", "fast", "slow"}
 
 
@@ -90,11 +91,6 @@ class FinolixConfig:
                 _rotation(m, where_m, m["rot_dim"], unread)
                 if m["rot"]["dims"] != m["rot_dim"]:
                     raise ConfigError(f"config.json: {where_m}.rot.dims must equal rot_dim")
-                mask = m.get("mask")
-                if mask is not None:
-                    _unknown(mask, {"size"}, where_m + ".mask.", unread)
-                    if _take(mask, "size", int) <= 0:
-                        raise ConfigError(f"config.json: {where_m}.mask.size must be positive")
             elif kind == "attention":
                 _unknown(m, _ATTENTION, where_m + ".", unread)
                 _positive(m, ("heads", "kv_heads", "dim", "vdim"), where_m)
@@ -105,6 +101,11 @@ class FinolixConfig:
             else:
                 raise ConfigError(f"config.json: {where}.type {kind!r} is not a mixer of this design "
                                   f"(known: 'latent_attention', 'attention')")
+            mask = m.get("mask")
+            if mask is not None:
+                _unknown(mask, {"size"}, where_m + ".mask.", unread)
+                if _take(mask, "size", int) <= 0:
+                    raise ConfigError(f"config.json: {where_m}.mask.size must be positive")
             f = layer.get("mlp")
             if f is not None:
                 if f.get("kind") == "dense":
@@ -124,8 +125,9 @@ class FinolixConfig:
                                       f"('dense', 'moe' or null)")
             j = layer.get("weights_of")
             if j is not None:
-                if not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < i or "weights_of" in layers[j]:
-                    raise ConfigError(f"config.json: {where}.weights_of must name an earlier layer with tensors of its own")
+                if not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < len(layers) or j == i or \
+                        layers[j].get("weights_of") is not None:
+                    raise ConfigError(f"config.json: {where}.weights_of must name another layer with tensors of its own")
                 mine = {k: v for k, v in layer.items() if k != "weights_of"}
                 if mine != layers[j]:
                     raise ConfigError(f"config.json: {where} borrows layer {j}'s weights but describes another layer")

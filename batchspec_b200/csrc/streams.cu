@@ -28,22 +28,30 @@ __global__ void stream_expand_kernel(const float* __restrict__ src, float* __res
   }
 }
 
-// The new streams of one column: old[] in, fresh[] out.
+// The new streams of one column: old[] in, fresh[] out.  SC > 0: the number of streams is known at compile time.
+template <int SC>
 __device__ __forceinline__ void join_column(const float* old, float y, const float* mixw, int S, float* fresh) {
-  for (int t = 0; t < S; ++t) {
+#pragma unroll
+  for (int t = 0; t < (SC > 0 ? SC : S); ++t) {
     float acc = 0.f;
-    for (int s = 0; s < S; ++s) acc += mixw[s * S + t] * old[s];
+#pragma unroll
+    for (int s = 0; s < (SC > 0 ? SC : S); ++s) acc += mixw[s * S + t] * old[s];
     fresh[t] = acc + mixw[S * S + t] * y;
   }
 }
 
-// One block per token.  u is kept in shared memory between the sum of squares and the scaling.
-template <typename TD, typename TO>
+// One block per token.  u is kept in shared memory between the sum of squares and the scaling.  SC: the number of
+// streams when it is 1, 2, 3, 4 or 8 (loops unrolled, a column's streams in registers), 0: any number up to 16.
+// VEC: four columns per thread and pass (d a multiple of 4).
+template <typename TD, typename TO, int SC, bool VEC>
 __global__ void stream_norm_kernel(float* __restrict__ x, const TD* __restrict__ pending,
                                    const float* __restrict__ vec, const float* __restrict__ mixw,
                                    const float* __restrict__ read, const void* __restrict__ weight, int w_dtype,
-                                   TO* __restrict__ out, int S, int d, float eps) {
+                                   TO* __restrict__ out, int S_rt, int d, float eps) {
   bspec::pdl_prologue(71);
+  constexpr int SMAX = SC > 0 ? SC : MAX_STREAMS;
+  constexpr int W = VEC ? 4 : 1;
+  const int S = SC > 0 ? SC : S_rt;
   extern __shared__ float u_row[];                // [d]
   __shared__ float coef[MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS];
   __shared__ float scratch[32];
@@ -56,23 +64,50 @@ __global__ void stream_norm_kernel(float* __restrict__ x, const TD* __restrict__
   const float* rd = coef + MAX_STREAMS * MAX_STREAMS + MAX_STREAMS;
   float* xt = x + t * S * d;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float cur[MAX_STREAMS];
-    for (int s = 0; s < S; ++s) cur[s] = xt[(size_t)s * d + i];
+  for (int i = W * threadIdx.x; i < d; i += W * blockDim.x) {
+    float cur[W][SMAX];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) {
+      if (s < S) {
+        if (VEC) {
+          const float4 v = *reinterpret_cast<const float4*>(xt + (size_t)s * d + i);
+          cur[0][s] = v.x; cur[W > 1 ? 1 : 0][s] = v.y; cur[W > 1 ? 2 : 0][s] = v.z; cur[W > 1 ? 3 : 0][s] = v.w;
+        } else {
+          cur[0][s] = xt[(size_t)s * d + i];
+        }
+      }
+    }
     if (pending != nullptr) {
-      const float y = to_f32(pending[t * d + i]) * (vec != nullptr ? vec[i] : 1.f);
-      float fresh[MAX_STREAMS];
-      join_column(cur, y, coef, S, fresh);
-      for (int s = 0; s < S; ++s) {
-        cur[s] = fresh[s];
-        xt[(size_t)s * d + i] = fresh[s];
+#pragma unroll
+      for (int c = 0; c < W; ++c) {
+        const float y = to_f32(pending[t * d + i + c]) * (vec != nullptr ? vec[i + c] : 1.f);
+        float fresh[SMAX];
+        join_column<SC>(cur[c], y, coef, S, fresh);
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+          if (s < S) cur[c][s] = fresh[s];
+      }
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s) {
+        if (s < S) {
+          if (VEC)
+            *reinterpret_cast<float4*>(xt + (size_t)s * d + i) =
+                make_float4(cur[0][s], cur[W > 1 ? 1 : 0][s], cur[W > 1 ? 2 : 0][s], cur[W > 1 ? 3 : 0][s]);
+          else
+            xt[(size_t)s * d + i] = cur[0][s];
+        }
       }
     }
     if (read != nullptr) {
-      float u = 0.f;
-      for (int s = 0; s < S; ++s) u += rd[s] * cur[s];
-      u_row[i] = u;
-      ss += u * u;
+#pragma unroll
+      for (int c = 0; c < W; ++c) {
+        float u = 0.f;
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+          if (s < S) u += rd[s] * cur[c][s];
+        u_row[i + c] = u;
+        ss += u * u;
+      }
     }
   }
   if (read == nullptr) return;
@@ -99,7 +134,7 @@ __global__ void stream_gather_kernel(const float* __restrict__ x, const TD* __re
     if (pending != nullptr) {
       const float y = to_f32(pending[t * d + i]) * (vec != nullptr ? vec[i] : 1.f);
       float fresh[MAX_STREAMS];
-      join_column(cur, y, coef, S, fresh);
+      join_column<0>(cur, y, coef, S, fresh);
       for (int s = 0; s < S; ++s) cur[s] = fresh[s];
     }
     float sum = 0.f;
@@ -126,18 +161,35 @@ BSPEC_API int bspec_stream_norm(float* x, const void* pending, int pending_dtype
     return (int)cudaErrorInvalidValue;
   const size_t smem = (size_t)d * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-#define LN(TD, TO)                                                                                                  \
+  const bool v4 = d % 4 == 0;
+  const int cols = v4 ? d / 4 : d;
+  const int threads = cols >= 512 ? 512 : (cols >= 256 ? 256 : 128);
+#define LN3(TD, TO, SC, V)                                                                                          \
   do {                                                                                                              \
     if (smem > 48 * 1024)                                                                                           \
-      cudaFuncSetAttribute(stream_norm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-    BSPEC_LAUNCH((stream_norm_kernel<TD, TO>), n, threads, smem, stream, x, (const TD*)pending, vec, mixw, read,    \
-                 weight, w_dtype, (TO*)out, S, d, eps);                                                             \
+      cudaFuncSetAttribute(stream_norm_kernel<TD, TO, SC, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                           (int)smem);                                                                              \
+    BSPEC_LAUNCH((stream_norm_kernel<TD, TO, SC, V>), n, threads, smem, stream, x, (const TD*)pending, vec, mixw,   \
+                 read, weight, w_dtype, (TO*)out, S, d, eps);                                                       \
+  } while (0)
+#define LN2(TD, TO, SC) do { if (v4) LN3(TD, TO, SC, true); else LN3(TD, TO, SC, false); } while (0)
+#define LN(TD, TO)                                                                                                  \
+  do {                                                                                                              \
+    switch (S) {                                                                                                    \
+      case 1: LN2(TD, TO, 1); break;                                                                                \
+      case 2: LN2(TD, TO, 2); break;                                                                                \
+      case 3: LN2(TD, TO, 3); break;                                                                                \
+      case 4: LN2(TD, TO, 4); break;                                                                                \
+      case 8: LN2(TD, TO, 8); break;                                                                                \
+      default: LN3(TD, TO, 0, false); break;                                                                        \
+    }                                                                                                               \
   } while (0)
   if (pending_dtype == BSPEC_F32 && out_dtype == BSPEC_F32) LN(float, float);
   else if (pending_dtype == BSPEC_BF16 && out_dtype == BSPEC_BF16) LN(__nv_bfloat16, __nv_bfloat16);
   else if (pending_dtype == BSPEC_F32 && out_dtype == BSPEC_BF16) LN(float, __nv_bfloat16);
   else LN(__nv_bfloat16, float);
+#undef LN3
+#undef LN2
 #undef LN
   return BSPEC_LAUNCH_CHECK();
 }

@@ -52,7 +52,7 @@ def build_finolix(cfg: FinolixConfig) -> ModelSpec:
             mixer = PartSpec("sink_attention", dict(
                 dim=d, n_heads=m["heads"], n_kv_heads=m["kv_heads"], head_dim=m["dim"], v_dim=m["vdim"],
                 scale=m["scale"], position=position, qk_norm_eps=cfg.norm_eps, qk_norm_weight=True,
-                qk_norm_first=True, gate="head"))
+                qk_norm_first=True, gate="head", window=(m.get("mask") or {}).get("size")))
             names.update({f"mixer.{k}": p + "mix." + k for k in ("q", "k", "v", "g", "o")})
             names.update({"mixer.q_norm": p + "mix.q.norm", "mixer.k_norm": p + "mix.k.norm"})
         parts = {"norm1": norm, "mixer": mixer, "scale1": scale}

@@ -657,7 +657,137 @@ def tokolorn_kernels_alone(z, pk, iters=20):
     return out
 
 
+FINOLIX_SIZES = {
+    # the Vabanex sizes (width, heads, head sizes, ranks, experts) with a window on the latent layers and four streams
+    "w2048": dict(VABANEX_SIZES["w2048"], window=1024, streams=4),
+    "w4096": dict(VABANEX_SIZES["w4096"], window=1024, streams=4),
+}
+
+
+def finolix_config_json(z, layers, vocab=32000):
+    """Latent attention (window, sink) and gated grouped-query attention in turn; the first layer's feed-forward is
+    the dense one, the others are routed (as in the Vabanex model of equal size, whose experts have two matrices
+    where these have three)."""
+    lat = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot"], vdim=z["vdim"], q_rank=z["q_rank"],
+               kv_rank=z["kv_rank"], scale=(z["dim"] + z["rot"]) ** -0.5, mask=dict(size=z["window"]),
+               rot=dict(base=10000.0, dims=z["rot"], scaling=dict(factor=40.0, original=4096, fast=32.0, slow=1.0)))
+    att = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=128, vdim=128, scale=128 ** -0.5,
+               rot=dict(base=500000.0, dims=64))
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]))
+    dense = dict(kind="dense", ff=z["dense_ff"])
+    return dict(architecture="Finolix", vocab=vocab, width=z["width"], norm=dict(eps=1e-5), streams=z["streams"],
+                layers=[dict(type="latent_attention" if i % 2 == 0 else "attention", mixer=lat if i % 2 == 0 else att,
+                             mlp=dense if i == 0 else moe) for i in range(layers)])
+
+
+def finolix_kernels_alone(z, pk, iters=20):
+    """The design's own kernels by themselves, each beside its like at equal sizes: latent attention with the window
+    and the sink against the same kernel without them (a prompt of 4,096 tokens: FLOP/s over the visible pairs
+    against the measured product peak; a decode step of 64 requests x 4,096 entries: bytes of visible entries
+    against the measured copy rate); the join, read and norm over the streams against add + RMS norm (bytes); the
+    q/k/v preparation with weighted head norms against the one without; the gate per head; routed gated experts
+    against routed GELU experts (FLOP/s of the two or three matrices of the chosen experts)."""
+    import torch
+    from types import SimpleNamespace
+    from batchspec_b200.kernels import ops
+    from batchspec_b200.parts.base import FEED_FORWARDS, PartSpec, Runtime, build_part
+    dev = "cuda:0"
+    Hh, R, Pd, ps, W, S, d = z["heads"], z["kv_rank"], z["rot"], 16, z["window"], z["streams"], z["width"]
+    out = {}
+    sinks = torch.linspace(-1.0, 1.0, Hh, device=dev)
+
+    def step_ctx(q_lens, ctx_len):
+        n, B = sum(q_lens), len(q_lens)
+        pages_per = -(-ctx_len // ps)
+        qo = torch.tensor([0] + list(__import__("itertools").accumulate(q_lens)), dtype=torch.int32, device=dev)
+        pos = torch.cat([torch.arange(ctx_len - q, ctx_len) for q in q_lens]).to(dev, torch.int32)
+        ent = torch.cat([torch.full((q,), i) for i, q in enumerate(q_lens)]).to(dev, torch.int32)
+        ctx = SimpleNamespace(qo_indptr=qo, positions=pos, tok_entry=ent, n_entries=B, n_tokens=n, max_q_len=max(q_lens),
+                              max_kv_len=ctx_len, kv_len=torch.full((B,), ctx_len, dtype=torch.int32, device=dev),
+                              extras={"min_q_len": min(q_lens)})
+        tables = SimpleNamespace(kv_indptr=torch.arange(B + 1, dtype=torch.int32, device=dev) * pages_per,
+                                 kv_indices=torch.randperm(B * pages_per, device=dev).to(torch.int32), page_size=ps)
+        return ctx, tables, n, B, pages_per
+
+    for name, q_lens, ctx_len in (("prompt_4096", [4096], 4096), ("decode_64x4096", [1] * 64, 4096)):
+        ctx, tables, n, B, pages_per = step_ctx(q_lens, ctx_len)
+        cache = torch.randn(B * pages_per, 1, ps * (R + Pd), device=dev).bfloat16()
+        ql = torch.randn(Hh, n, R, device=dev).bfloat16()
+        qr = torch.randn(n, Hh, Pd, device=dev).bfloat16()
+        o = torch.empty(Hh, n, R, device=dev, dtype=torch.bfloat16)
+        for label, win, sk in (("window_sink", W, sinks), ("sink", 0, sinks), ("causal", 0, None)):
+            ms = _time(lambda: ops.latent_attention(ql, qr, o, cache, ctx, tables, Hh, R, Pd, 0.05, window=win, sink=sk), iters)
+            span = win or (1 << 30)
+            pairs = sum(min(p + 1, span) for p in range(ctx_len - q_lens[0], ctx_len)) * len(q_lens)
+            if name.startswith("prompt"):
+                flops = 2.0 * Hh * (R + Pd + R) * pairs
+                out[f"latent_{name}_{label}"] = dict(ms=round(ms, 4), tflops=round(flops / ms / 1e9, 1),
+                                                     frac_of_measured=round(flops / ms / 1e9 / pk["bf16_tflops"], 4))
+            else:
+                nbytes = pairs * (R + Pd) * 2
+                out[f"latent_{name}_{label}"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+                                                     frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    # the streams' join + read + norm against add + RMS norm, 4,096 rows and 64 rows
+    for n in (4096, 64):
+        x = torch.randn(n, S, d, device=dev)
+        one = torch.randn(n, d, device=dev)
+        y = torch.randn(n, d, device=dev).bfloat16()
+        vec, w = torch.ones(d, device=dev), torch.ones(d, device=dev)
+        mixw = torch.cat([torch.eye(S, device=dev).reshape(-1), torch.ones(S, device=dev)]).contiguous()
+        rd = torch.full((S,), 1.0 / S, device=dev)
+        o = torch.empty(n, d, device=dev, dtype=torch.bfloat16)
+        ms = _time(lambda: ops.stream_norm(x, y, vec, mixw, rd, w, 1e-5, o), iters)
+        nbytes = n * d * (S * 8 + 2 + 2)
+        out[f"stream_norm_{n}"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+                                       frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+        ms = _time(lambda: ops.add_rmsnorm(one, y, w, 1e-5, o, 1.0, True, vec), iters)
+        nbytes = n * d * (8 + 2 + 2)
+        out[f"add_rmsnorm_{n}"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+                                       frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    # q/k/v preparation with weighted head norms before the rotation against the one without; the gate per head
+    Hq, G, hd = z["heads"], z["kv_heads"], 128
+    ctx, tables, n, B, pages_per = step_ctx([4096], 4096)
+    cache = torch.zeros(pages_per, 2, ps * G * hd, device=dev, dtype=torch.bfloat16)
+    width = (Hq + 2 * G) * hd
+    qkv32 = torch.randn(n, width, device=dev)
+    nw = torch.ones(hd, device=dev, dtype=torch.bfloat16)
+    freq = ops.rope_frequency_table(torch.pow(torch.tensor(500000.0, dtype=torch.float64), -torch.arange(0, 32, dtype=torch.float64) * 2 / 64), dev)
+    nbytes = n * width * (4 + 2)
+    for label, kw in (("qkv_prepare_weighted_norm_4096", dict(q_norm=nw, k_norm=nw, norm_first=True)), ("qkv_prepare_4096", {})):
+        ms = _time(lambda: ops.qkv_prepare(qkv32, Hq, G, hd, hd, None, freq, 64, False, 1.0, 1e-5 if kw else 0.0, ctx.positions,
+                                           ctx.tok_entry, tables.kv_indptr, tables.kv_indices, cache, ps, **kw), iters)
+        out[label] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    heads = torch.randn(n, Hq * hd, device=dev).bfloat16()
+    gate = torch.randn(n, Hq, device=dev)
+    gate_all = torch.randn(n, Hq * hd, device=dev)
+    o = torch.empty_like(heads)
+    ms = _time(lambda: ops.gate_heads(heads.view(n, Hq, hd).transpose(0, 1), gate, o), iters)
+    out["gate_per_head_4096"] = dict(ms=round(ms, 4), frac_of_measured=round(n * Hq * hd * 4 / ms / 1e6 / pk["hbm_gbs"], 4))
+    ms = _time(lambda: ops.gate_mul(heads, gate_all, o), iters)
+    out["gate_per_number_4096"] = dict(ms=round(ms, 4), frac_of_measured=round(n * Hq * hd * 8 / ms / 1e6 / pk["hbm_gbs"], 4))
+    # routed experts: gated (three matrices) against GELU (two), the router included
+    rt = Runtime(torch.bfloat16, torch.device(dev))
+    E, top, ff = z["experts"], z["top"], z["expert_ff"]
+    glu = build_part(FEED_FORWARDS, PartSpec("routed_glu", dict(dim=d, intermediate=ff, n_experts=E, top=top)), rt)
+    gelu = build_part(FEED_FORWARDS, PartSpec("routed_gelu", dict(dim=d, intermediate=ff, n_experts=E, top=top, n_groups=z["groups"],
+                                                                  keep_groups=z["keep"])), rt)
+    for part, mats in ((glu, 3), (gelu, 2)):
+        part.bind({k: (torch.randn(ps_.shape, device=dev) * 0.02).bfloat16() for k, ps_ in part.param_specs().items()})
+        for n in (4096, 64):
+            x = torch.randn(n, d, device=dev).bfloat16()
+            ms = _time(lambda: part.forward(x, None), iters)
+            flops = 2.0 * n * top * mats * ff * d
+            rec = dict(ms=round(ms, 4), tflops=round(flops / ms / 1e9, 1), frac_of_measured=round(flops / ms / 1e9 / pk["bf16_tflops"], 4))
+            if n == 64:                     # decode: the weights of the experts that were chosen are read once
+                nbytes = min(E, n * top) * mats * ff * d * 2
+                rec["weights_frac_of_measured"] = round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4)
+            out[f"{part.kind}_{n}"] = rec
+        del part
+    return out
+
+
 DESIGNS = {
+    "finolix": (FINOLIX_SIZES, finolix_config_json, finolix_kernels_alone, "kernels_alone"),
     "tokolorn": (TOKOLORN_SIZES, tokolorn_config_json, tokolorn_kernels_alone, "kernels_alone"),
     "vabanex": (VABANEX_SIZES, vabanex_config_json, latent_attention_alone, "latent_attention_alone"),
     "lupusun": (LUPUSUN_SIZES, lupusun_config_json, lupusun_kernels_alone, "kernels_alone"),
@@ -681,6 +811,8 @@ def run_design(a) -> int:
         models = [(a.design, config_json(z, layers)), ("llama", llama_config_json(z, layers))]
         if a.design == "tokolorn":        # its closest model, the other one with recurrent state beside attention
             models.append(("lupusun", lupusun_config_json(z, layers)))
+        if a.design == "finolix":         # its closest model, the other one with latent attention and routed experts
+            models.append(("vabanex", vabanex_config_json(z, layers)))
         for label, cj in models:
             cfg = config_from_json_dict(cj)
             eng = Engine(dtype="bfloat16", device="cuda:0")
@@ -762,7 +894,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no prefill, b1, b64, e2e)")
     ap.add_argument("--skip-workloads", action="store_true",
                     help="leave out e2e at batch 64 and the 3B / long-context workloads (about a minute)")
-    ap.add_argument("--design", default=None, choices=["vabanex", "lupusun", "tokolorn"],
+    ap.add_argument("--design", default=None, choices=["vabanex", "lupusun", "tokolorn", "finolix"],
                     help="instead of the headline workload: this design at real layer sizes beside the Llama model of equal size")
     a = ap.parse_args()
     if a.impl == "reference":

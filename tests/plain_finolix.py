@@ -193,3 +193,34 @@ def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: Sequence[int
     x = x if xs is None else sum(xs)
     logits = one_plus_norm(x, tensors["final.norm"], eps) @ f64(tensors["head"]).T
     return logits, torch.stack(after)
+
+
+# ---------------------------------------------------------------------------- model folders
+
+def read_tensors(path) -> Dict[str, torch.Tensor]:
+    """A safetensors file: an 8-byte little-endian length, that many bytes of JSON (name -> dtype, shape, offsets), the
+    data.  bfloat16 comes back as float32 with the same values."""
+    import json
+    import struct
+    import numpy as np
+    raw = open(path, "rb").read()
+    (n,) = struct.unpack("<Q", raw[:8])
+    data = raw[8 + n:]
+    out = {}
+    for name, meta in json.loads(raw[8:8 + n]).items():
+        if name == "__metadata__":
+            continue
+        lo, hi = meta["data_offsets"]
+        if meta["dtype"] == "BF16":
+            arr = (np.frombuffer(data[lo:hi], dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+        else:
+            arr = np.frombuffer(data[lo:hi], dtype={"F32": np.float32, "I32": np.int32}[meta["dtype"]]).copy()
+        out[name] = torch.from_numpy(arr.copy()).reshape(meta["shape"])
+    return out
+
+
+def read_model_folder(folder):
+    import json
+    from pathlib import Path
+    folder = Path(folder)
+    return json.loads((folder / "config.json").read_text()), read_tensors(folder / "model.safetensors")
