@@ -15,6 +15,7 @@
 // Cache layout of a layer: [pages][page_size][R + P].
 #include "common.cuh"
 #include <math.h>
+#include <stdint.h>
 using namespace bspec;
 
 namespace {
@@ -174,6 +175,31 @@ __global__ void gate_heads_kernel(const T* __restrict__ v, long long v_head, lon
   }
 }
 
+// The same for bfloat16 with eight numbers (16 bytes) per thread: V, both strides of v and every address multiples
+// of 8 numbers; a thread's eight numbers lie in one head, so it forms that head's sigmoid once.  Grid-stride over
+// all (token, piece) pairs.
+__global__ void gate_heads_bf16x8_kernel(const __nv_bfloat16* __restrict__ v, long long v_head, long long v_row,
+                                         const float* __restrict__ gate, int ld, __nv_bfloat16* __restrict__ out,
+                                         int H, int V, long long total) {
+  bspec::pdl_prologue(42);
+  const int per_row = H * V / 8, per_head = V / 8;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / per_row;
+    const int piece = (int)(idx - t * per_row);
+    const int h = piece / per_head, j = (piece - h * per_head) * 8;
+    const float g = 1.f / (1.f + expf(-gate[t * ld + h]));
+    uint4 x = *reinterpret_cast<const uint4*>(v + (size_t)h * v_head + (size_t)t * v_row + j);
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(p[k]);
+      p[k] = __floats2bfloat162_rn(f.x * g, f.y * g);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * H * V + (size_t)piece * 8) = x;
+  }
+}
+
 }  // namespace
 
 BSPEC_API int bspec_latent_prepare(const float* down, int n, int ld, int q_off, int Rq, int kv_off, int R, int P,
@@ -225,6 +251,14 @@ BSPEC_API int bspec_latent_attention_generic(const void* ql, long long ql_row, l
 BSPEC_API int bspec_gate_heads(const void* v, long long v_head, long long v_row, const float* gate, int ld, void* out,
                                int dtype, int n, int H, int V, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (dtype != BSPEC_F32 && V % 8 == 0 && v_head % 8 == 0 && v_row % 8 == 0 &&
+      !((reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15)) {
+    const long long total = (long long)n * (H * V / 8);
+    const long long want = (total + 255) / 256, cap = (long long)bspec::sm_count() * 16;
+    BSPEC_LAUNCH((gate_heads_bf16x8_kernel), (int)(want > cap ? cap : want), 256, 0, stream, (const __nv_bfloat16*)v,
+                 v_head, v_row, gate, ld, (__nv_bfloat16*)out, H, V, total);
+    return BSPEC_LAUNCH_CHECK();
+  }
   const int threads = H * V >= 1024 ? 256 : 128;
   if (dtype == BSPEC_F32)
     BSPEC_LAUNCH((gate_heads_kernel<float>), n, threads, 0, stream, (const float*)v, v_head, v_row, gate, ld, (float*)out, H, V);

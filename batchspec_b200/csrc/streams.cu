@@ -28,6 +28,28 @@ __global__ void stream_expand_kernel(const float* __restrict__ src, float* __res
   }
 }
 
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&f)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&f)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[4]) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x), b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+  f[0] = __low2float(a); f[1] = __high2float(a); f[2] = __low2float(b); f[3] = __high2float(b);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const float (&f)[4]);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float (&f)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  uint2 v;
+  v.x = *reinterpret_cast<const uint32_t*>(&a);
+  v.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
 // The new streams of one column: old[] in, fresh[] out.  SC > 0: the number of streams is known at compile time.
 template <int SC>
 __device__ __forceinline__ void join_column(const float* old, float y, const float* mixw, int S, float* fresh) {
@@ -78,9 +100,17 @@ __global__ void stream_norm_kernel(float* __restrict__ x, const TD* __restrict__
       }
     }
     if (pending != nullptr) {
+      float yv[W], vv[W];
+      if (VEC) {
+        load4<TD>(pending + t * d + i, *reinterpret_cast<float(*)[4]>(yv));
+        if (vec != nullptr) load4<float>(vec + i, *reinterpret_cast<float(*)[4]>(vv));
+      } else {
+        yv[0] = to_f32(pending[t * d + i]);
+        if (vec != nullptr) vv[0] = vec[i];
+      }
 #pragma unroll
       for (int c = 0; c < W; ++c) {
-        const float y = to_f32(pending[t * d + i + c]) * (vec != nullptr ? vec[i + c] : 1.f);
+        const float y = yv[c] * (vec != nullptr ? vv[c] : 1.f);
         float fresh[SMAX];
         join_column<SC>(cur[c], y, coef, S, fresh);
 #pragma unroll
@@ -112,6 +142,15 @@ __global__ void stream_norm_kernel(float* __restrict__ x, const TD* __restrict__
   }
   if (read == nullptr) return;
   const float r = 1.f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+  if (VEC) {                                      // a thread scales the columns it formed itself
+    for (int i = W * threadIdx.x; i < d; i += W * blockDim.x) {
+      float y[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) y[c] = u_row[i + c] * r * load_as_f32(weight, w_dtype, i + c);
+      store4<TO>(out + t * d + i, y);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < d; i += blockDim.x)
     out[t * d + i] = from_f32<TO>(u_row[i] * r * load_as_f32(weight, w_dtype, i));
 }
@@ -163,7 +202,9 @@ BSPEC_API int bspec_stream_norm(float* x, const void* pending, int pending_dtype
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   const bool v4 = d % 4 == 0;
   const int cols = v4 ? d / 4 : d;
-  const int threads = cols >= 512 ? 512 : (cols >= 256 ? 256 : 128);
+  // at most 256 threads: with a column's streams in registers, several smaller blocks share an SM and cover each
+  // other's barrier between the two passes
+  const int threads = cols >= 256 ? 256 : 128;
 #define LN3(TD, TO, SC, V)                                                                                          \
   do {                                                                                                              \
     if (smem > 48 * 1024)                                                                                           \
