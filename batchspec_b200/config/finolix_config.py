@@ -128,9 +128,8 @@ class FinolixConfig:
                 if not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < len(layers) or j == i or \
                         layers[j].get("weights_of") is not None:
                     raise ConfigError(f"config.json: {where}.weights_of must name another layer with tensors of its own")
-                mine = {k: v for k, v in layer.items() if k != "weights_of"}
-                if mine != layers[j]:
-                    raise ConfigError(f"config.json: {where} borrows layer {j}'s weights but describes another layer")
+                if layers[j].get("type") != kind:
+                    raise ConfigError(f"config.json: {where} borrows layer {j}'s weights but is of another type")
             out.append(copy.deepcopy(layer))
         cfg = cls(architecture=d.get("architecture") or (d.get("architectures") or [None])[0],
                   vocab_size=_take(d, "vocab", int), width=_take(d, "width", int), norm_eps=_take(norm, "eps", float),

@@ -171,7 +171,7 @@ def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: Sequence[int
     after = []
     rnd = round_input or (lambda t: t)
     for i, layer in enumerate(config["layers"]):
-        p = f"l{layer.get('weights_of', i)}."
+        p = f"l{i if layer.get('weights_of') is None else layer['weights_of']}."
         subs = [(1, "mix.", lambda u, w: (latent_attention if layer["type"] == "latent_attention" else gated_attention)(
             u, w, layer["mixer"], eps))]
         f = layer.get("mlp")

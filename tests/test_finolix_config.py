@@ -60,6 +60,7 @@ def test_reader_takes_every_size_from_the_file_and_round_trips():
     lambda d: d["layers"][1]["mlp"]["router"].update(top=6), lambda d: d["layers"][1]["mlp"].update(kind="glu"),
     lambda d: d.update(streams=0), lambda d: d.update(streams=17), lambda d: d["layers"][2].update(weights_of=2),
     lambda d: d["layers"][2].update(weights_of=1), lambda d: d["norm"].update(eps=0.0),
+    lambda d: d["layers"][2].update(weights_of=5),
 ])
 def test_reader_refuses_what_cannot_be_run(break_it):
     layers = [latent(), attention()]
