@@ -49,6 +49,7 @@ struct GemmParams {
                          // 1: silu(gate) * up;  2: g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, +-limit);
                          // 3: relu(gate) * up
   float glu_alpha, glu_limit;
+  int act;               // a plain activation on every output (no gate): 0 none, 1 the square of relu
   int prefetch_kb;       // K blocks of weights (beyond the stages) to pull into the L2 before waiting on the predecessor
   // fused q/k/v projection (rope_freq != nullptr): tile t of W is head t (q heads, then k heads, then v heads)
   const float* rope_freq;    // [2][64] frequencies as two floats each (see elementwise.cu, rope_sincos)
@@ -84,6 +85,12 @@ __device__ __forceinline__ float glu_combine(int kind, float alpha, float limit,
   if (kind == 3) return fmaxf(g, 0.f) * u;
   if (kind == 4) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;   // gelu, tanh form
   return g / (1.f + expf(-g)) * u;
+}
+
+// A plain activation on one output (GemmParams::act).
+__device__ __forceinline__ float unary_act(int kind, float x) {
+  if (kind == 1) { const float r = fmaxf(x, 0.f); return r * r; }
+  return x;
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS)
@@ -223,6 +230,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (ra < p.M) {
             const int n0 = tile_b * p.bn + c0;
             const size_t base = (size_t)ra * p.N + n0;
+            if (p.act) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(unary_act(p.act, __uint_as_float(v[j])));
+            }
             if (!p.out_f32 && n0 + 16 <= p.N && (p.N % 8) == 0) {
               uint32_t w[8];
 #pragma unroll
@@ -245,7 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int tok = tile_b * p.bn + c0 + j;
-              if (tok < p.M) store_out(p.C, p.out_f32, (size_t)tok * p.N + ra, __uint_as_float(v[j]));
+              if (tok < p.M) store_out(p.C, p.out_f32, (size_t)tok * p.N + ra, unary_act(p.act, __uint_as_float(v[j])));
             }
           }
         } else {
@@ -308,6 +319,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                   if (p.glu) acc_u += u[t][s];
                 }
               if (p.glu) acc = glu_combine(p.glu, p.glu_alpha, p.glu_limit, acc, acc_u);
+              else if (p.act) acc = unary_act(p.act, acc);
             }
             res[t] = acc;
           }
@@ -440,7 +452,7 @@ struct RopeEpilogue {
 
 static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu, int* status,
                        int sm_count, const RopeEpilogue* rope, cudaStream_t stream, float glu_alpha = 1.f,
-                       float glu_limit = 0.f) {
+                       float glu_limit = 0.f, int act = 0) {
   int plan[5];
   if (bspec_gemm_tc_plan(M, N, K, sm_count, plan) < 0) return (int)cudaErrorInvalidValue;
   if (glu && (N % 16 != 0)) return (int)cudaErrorInvalidValue;
@@ -448,6 +460,8 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
   p.C = C; p.status = status;
   p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu == 2 ? 2 : (glu == 3 ? 3 : (glu == 4 ? 4 : (glu ? 1 : 0)));
   p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
+  if (act && (glu || rope != nullptr)) return (int)cudaErrorInvalidValue;
+  p.act = act;
   p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
   p.rope_freq = nullptr; p.positions = p.tok_entry = p.kv_indptr = p.kv_indices = nullptr; p.cache = nullptr;
   p.Hq = p.Hkv = p.page_size = p.interleaved = p.write_kv = 0;
@@ -515,6 +529,13 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
 BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu,
                             int* status, int sm_count, cudaStream_t stream) {
   return launch_gemm(X, W, C, M, N, K, out_f32, glu, status, sm_count, nullptr, stream);
+}
+
+// C = act(X W^T) with a plain activation on every output: act 1 = the square of relu.
+BSPEC_API int bspec_gemm_tc_act(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int act,
+                                int* status, int sm_count, cudaStream_t stream) {
+  if (act != 1) return (int)cudaErrorInvalidValue;
+  return launch_gemm(X, W, C, M, N, K, out_f32, 0, status, sm_count, nullptr, stream, 1.f, 0.f, act);
 }
 
 // The same with the clamped gated activation in the epilogue: C[M, N/2] = g sigmoid(alpha g) (u + 1) with

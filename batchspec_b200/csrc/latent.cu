@@ -4,7 +4,7 @@
 // rotated part (P numbers); score(i, j) = scale * ([ql | qr] . entry_j), causal softmax, and the head's output
 // is sum_j p_j c_j (R numbers), which the caller multiplies by the head's value up-projection.  All heads read the
 // same entries.  ``window`` > 0: a query sees its own entry and the window - 1 before it; ``sink``: a logit per head
-// whose exponential joins the softmax denominator (no key, no value, not scaled).
+// that only enlarges the softmax's denominator (nothing is attended through it; ``scale`` does not touch it).
 //
 // Kernels here:
 //   latent_prepare      per token: RMS norm of the query latent, RMS norm of the key/value latent, rotation of kr

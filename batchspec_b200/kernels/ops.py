@@ -133,6 +133,7 @@ _SIGNATURES = {
                                           c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "bspec_gemm_tc_act": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "bspec_gemm_tc_clamped_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int,
                                   c_void_p],
     "bspec_gemm_tc_qkv_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -1111,6 +1112,27 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.T
     _check(lib.bspec_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32), 0,
                              _status_word(x.device).data_ptr(), sm_count(x.device), _stream()), "gemm_tc")
     return out
+
+
+PLAIN_ACTIVATIONS = {"relu2": (1, relu_squared_), "gelu": (0, gelu_erf_)}     # epilogue kind (0: none), in-place kernel
+
+
+def linear_act(x: torch.Tensor, w: torch.Tensor, activation: str) -> torch.Tensor:
+    """act(x w^T) with a plain activation on every output (``PLAIN_ACTIVATIONS``): one kernel with the activation in
+    the tcgen05 product's epilogue for decode-sized bfloat16 steps when the epilogue knows it, else the product and
+    the in-place activation kernel."""
+    epilogue, kernel = PLAIN_ACTIVATIONS[activation]
+    _require_cuda(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    if (epilogue and GLU_FUSION and x.dtype == torch.bfloat16 and K % 8 == 0 and M > 0 and x.is_contiguous()
+            and w.is_contiguous() and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        _check(load_library().bspec_gemm_tc_act(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, 0, epilogue,
+                                                _status_word(x.device).data_ptr(), sm_count(x.device), _stream()),
+               "gemm_tc_act")
+        return out
+    return kernel(linear(x, w))
 
 
 FUSE_QKV_ROPE = True       # decode-sized steps: rotary encoding and the cache append in the q/k/v product's epilogue

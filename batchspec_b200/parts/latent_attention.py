@@ -9,8 +9,8 @@ With h a token's normed input, H heads, per head ``dim`` unrotated and ``rot_dim
     out = Wo concat_h(sigmoid(Wg h)_h * sum_j softmax_j(score_h(i, .)) v_h(j))
 
 Options: ``gated`` False leaves the gate out; ``window`` W keeps the keys i - W + 1 .. i of query i (pages that the
-window has passed are given back); ``sink``: a learned logit per head whose exponential joins the softmax
-denominator, with no key and no value.
+window has passed are given back); ``sink``: a learned logit per head that only enlarges the softmax's denominator
+(nothing is attended through it, and ``scale`` does not touch it).
 
 Only [c | rot(kr)] is cached (one tensor per token, ``kv_rank + rot_dim`` numbers).  The per-head keys and values
 are never formed: since q_h . (Wuk_h c) = (Wuk_h^T q_h) . c, the unrotated query is taken into the latent space

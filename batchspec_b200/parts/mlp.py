@@ -99,9 +99,10 @@ class ClampedGLU(FeedForward):
 @register_part(FEED_FORWARDS, "mlp")
 class PlainMLP(FeedForward):
     """Two matrices and an activation between them: out = Wdown act(Wup x), no gate and no biases.
-    ``activation``: "relu2" (the square of relu) or "gelu" (the exact one)."""
+    ``activation``: "relu2" (the square of relu) or "gelu" (the exact one).  Decode-sized bfloat16 steps apply the
+    square of relu in the first product's epilogue."""
     graph_safe = True
-    ACTIVATIONS = {"relu2": ops.relu_squared_, "gelu": ops.gelu_erf_}
+    ACTIVATIONS = ops.PLAIN_ACTIVATIONS
 
     def __init__(self, runtime: Runtime, dim: int, intermediate: int, activation: str = "relu2"):
         self.runtime, self.dim, self.intermediate = runtime, int(dim), int(intermediate)
@@ -118,8 +119,6 @@ class PlainMLP(FeedForward):
 
     def forward(self, x, ctx):
         with bucket("mlp.up_proj"):
-            u = ops.linear(x, self.w1)
-        with bucket("mlp.act"):
-            self.ACTIVATIONS[self.activation](u)
+            u = ops.linear_act(x, self.w1, self.activation)
         with bucket("mlp.down_proj"):
             return ops.linear(u, self.w2)

@@ -172,7 +172,8 @@ def test_streams_join_read_norm_and_sum(ops, dtype, n, S, d):
 def test_squared_relu_feed_forward(ops, dtype):
     from batchspec_b200.parts.base import FEED_FORWARDS, PartSpec, Runtime, build_part
     g = torch.Generator(device=DEV).manual_seed(3)
-    for n, d, ff in ((5, 48, 40), (1, 100, 44), (70, 320, 192)):
+    # rows up to 8 with inner sizes that are multiples of 8 take the product with the activation in its epilogue
+    for n, d, ff in ((5, 48, 40), (1, 100, 44), (70, 320, 192), (1, 512, 1024), (8, 320, 200), (3, 2048, 8448), (9, 512, 1024)):
         part = build_part(FEED_FORWARDS, PartSpec("mlp", dict(dim=d, intermediate=ff)), Runtime(dtype, torch.device(DEV)))
         w = {"up": (0.2 * torch.randn(ff, d, device=DEV, generator=g)).to(dtype),
              "down": (0.2 * torch.randn(d, ff, device=DEV, generator=g)).to(dtype)}
