@@ -11,6 +11,8 @@
 //             sorted order holds slot perm[r]; inv[slot] = r), and the list of row tiles (expert, first row, rows)
 //   grouped   C[r, :] = act(A[src(r), :] . W[expert(r)]^T) over the tiles of the plan; every output element is one
 //             thread's sum over k in ascending order, so a row's result does not depend on where it was sorted to
+//             (act: GELU on the outputs, or none; the operand A may be gated instead: its rows are [gate | up] and
+//             silu(gate) * up is formed while they are staged, which is how gated experts run their down projection)
 //   combine   out[t, :] = sum_k weight[t, k] * Y[inv[t*top + k], :], k ascending, float32
 //
 // Nothing here reads a count on the host: grids are sized by upper bounds and surplus blocks leave at once, so the
@@ -221,12 +223,29 @@ moe_place_kernel(const int* __restrict__ ids, const int* __restrict__ rank, cons
 
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f)); }
 
+// A gated operand (``gated_a`` in the kernels below): the rows of A are [gate | up], 2 K numbers, and the product's
+// operand is silu(gate) * up, formed while a tile's rows are staged and rounded to A's type, as a kernel of its own
+// between the two products would have left it.
+__device__ __forceinline__ float silu_gate(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+__device__ __forceinline__ uint4 silu_gate8(const uint4& gv, const uint4& uv) {
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+  uint4 ov;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    o2[j] = __floats2bfloat162_rn(silu_gate(__low2float(g2[j]), __low2float(u2[j])),
+                                  silu_gate(__high2float(g2[j]), __high2float(u2[j])));
+  return ov;
+}
+
 // A [*, K] rows; row r of the sorted order reads A[perm[r] / top] when perm is given (the up projection), else
 // A[r] (the down projection).  W [E, N, K].  C [slots, N].  Thread tiles of TM x 4, 16 x 16 threads.
 template <typename T, typename TO, int BM, bool GELU>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const T* __restrict__ A, const int* __restrict__ perm, int top, const T* __restrict__ W,
-                   TO* __restrict__ C, int N, int K, const int* __restrict__ tiles, const int* __restrict__ n_tiles) {
+                   TO* __restrict__ C, int N, int K, const int* __restrict__ tiles, const int* __restrict__ n_tiles,
+                   int gated_a) {
   bspec::pdl_prologue(52);
   constexpr int BN = 64, BK = 16, TM = BM / 16, TN = 4;
   if ((int)blockIdx.y >= *n_tiles) return;
@@ -247,7 +266,16 @@ moe_grouped_kernel(const T* __restrict__ A, const int* __restrict__ perm, int to
   for (int k0 = 0; k0 < K; k0 += BK) {
     for (int idx = tid; idx < BM * BK; idx += 256) {
       const int r = idx / BK, k = k0 + idx % BK;
-      As[idx % BK][r] = (src[r] >= 0 && k < K) ? to_f32(A[(size_t)src[r] * K + k]) : 0.f;
+      float a = 0.f;
+      if (src[r] >= 0 && k < K) {
+        if (gated_a) {
+          const T* row = A + (size_t)src[r] * 2 * K;
+          a = to_f32(from_f32<T>(silu_gate(to_f32(row[k]), to_f32(row[K + k]))));
+        } else {
+          a = to_f32(A[(size_t)src[r] * K + k]);
+        }
+      }
+      As[idx % BK][r] = a;
     }
     for (int idx = tid; idx < BN * BK; idx += 256) {
       const int r = idx / BK, k = k0 + idx % BK;
@@ -300,7 +328,7 @@ template <typename TO, bool GELU>
 __global__ void __launch_bounds__(256)
 moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ perm, int top,
                   const __nv_bfloat16* __restrict__ W, TO* __restrict__ C, int N, int K, const int* __restrict__ tiles,
-                  const int* __restrict__ n_tiles) {
+                  const int* __restrict__ n_tiles, int gated_a) {
   bspec::pdl_prologue(55);
   constexpr int RMAX = 8;
   if ((int)blockIdx.y >= *n_tiles) return;
@@ -311,7 +339,12 @@ moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ p
   for (int idx = tid; idx < rows * K8; idx += 256) {
     const int r = idx / K8, c = idx - r * K8;
     const int src = perm != nullptr ? perm[row0 + r] / top : row0 + r;
-    As4[idx] = reinterpret_cast<const uint4*>(A + (size_t)src * K)[c];
+    if (gated_a) {
+      const uint4* row = reinterpret_cast<const uint4*>(A + (size_t)src * 2 * K);
+      As4[idx] = silu_gate8(row[c], row[K8 + c]);
+    } else {
+      As4[idx] = reinterpret_cast<const uint4*>(A + (size_t)src * K)[c];
+    }
   }
   __syncthreads();
   const __nv_bfloat16* We = W + (size_t)e * N * K;
@@ -367,7 +400,7 @@ template <typename TO, bool GELU, int RT>          // RT: token rows a tile may 
 __global__ void __launch_bounds__(256)
 moe_skinny_mma_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ perm, int top,
                       const __nv_bfloat16* __restrict__ W, TO* __restrict__ C, int N, int K,
-                      const int* __restrict__ tiles, const int* __restrict__ n_tiles) {
+                      const int* __restrict__ tiles, const int* __restrict__ n_tiles, int gated_a) {
   bspec::pdl_prologue(56);
   if ((int)blockIdx.y >= *n_tiles) return;
   extern __shared__ uint4 Xs[];                   // [RT][K / 8 + 1]: token rows (rows past the tile are zero)
@@ -379,7 +412,12 @@ moe_skinny_mma_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (r < rows) {
       const int src = perm != nullptr ? perm[row0 + r] / top : row0 + r;
-      v = reinterpret_cast<const uint4*>(A + (size_t)src * K)[c];
+      if (gated_a) {
+        const uint4* row = reinterpret_cast<const uint4*>(A + (size_t)src * 2 * K);
+        v = silu_gate8(row[c], row[K8 + c]);
+      } else {
+        v = reinterpret_cast<const uint4*>(A + (size_t)src * K)[c];
+      }
     }
     Xs[r * XS + c] = v;
   }
@@ -517,12 +555,13 @@ BSPEC_API int bspec_moe_plan(const int* ids, int slots, int E, int BM, int* perm
 
 BSPEC_API int bspec_moe_grouped(const void* A, const int* perm, int top, const void* W, void* C, int dtype,
                                 int out_dtype, int N, int K, const int* tiles, const int* n_tiles, int max_tiles,
-                                int BM, int gelu, cudaStream_t stream) {
+                                int BM, int act, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return 0;
+  const int gelu = act == 1, gated_a = act == 2;       // act: 0 none, 1 GELU on the outputs, 2 a gated operand A
   dim3 grid((N + 63) / 64, max_tiles);
   if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
 #define LK(T, TO, B, G) BSPEC_LAUNCH((moe_grouped_kernel<T, TO, B, G>), grid, 256, 0, stream, (const T*)A, perm, top, \
-                                     (const T*)W, (TO*)C, N, K, tiles, n_tiles)
+                                     (const T*)W, (TO*)C, N, K, tiles, n_tiles, gated_a)
 #define LB(T, TO) do { if (BM == 64) { if (gelu) LK(T, TO, 64, true); else LK(T, TO, 64, false); }                  \
                        else { if (gelu) LK(T, TO, 16, true); else LK(T, TO, 16, false); } } while (0)
   if (dtype == BSPEC_F32) LB(float, float);
@@ -535,9 +574,10 @@ BSPEC_API int bspec_moe_grouped(const void* A, const int* perm, int top, const v
 
 // Tiles of at most 8 rows (a plan made with BM = 8), bfloat16 operands, K a multiple of 8.
 BSPEC_API int bspec_moe_skinny(const void* A, const int* perm, int top, const void* W, void* C, int out_dtype, int N,
-                               int K, const int* tiles, const int* n_tiles, int max_tiles, int gelu,
+                               int K, const int* tiles, const int* n_tiles, int max_tiles, int act,
                                cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return 0;
+  const int gelu = act == 1, gated_a = act == 2;
   if (K % 8 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
     return (int)cudaErrorInvalidValue;
   dim3 grid((N + 63) / 64, max_tiles);
@@ -548,7 +588,7 @@ BSPEC_API int bspec_moe_skinny(const void* A, const int* perm, int top, const vo
   do {                                                                                                              \
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_skinny_kernel<TO, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     BSPEC_LAUNCH((moe_skinny_kernel<TO, G>), grid, 256, smem, stream, (const __nv_bfloat16*)A, perm, top,           \
-                 (const __nv_bfloat16*)W, (TO*)C, N, K, tiles, n_tiles);                                            \
+                 (const __nv_bfloat16*)W, (TO*)C, N, K, tiles, n_tiles, gated_a);                                   \
   } while (0)
   if (out_dtype == BSPEC_F32) { if (gelu) LS(float, true); else LS(float, false); }
   else { if (gelu) LS(__nv_bfloat16, true); else LS(__nv_bfloat16, false); }
@@ -558,9 +598,10 @@ BSPEC_API int bspec_moe_skinny(const void* A, const int* perm, int top, const vo
 
 // Tiles of at most `rows_per_tile` rows (8 or 16: a plan made with that BM), bfloat16 operands, K a multiple of 32.
 BSPEC_API int bspec_moe_skinny_mma(const void* A, const int* perm, int top, const void* W, void* C, int out_dtype,
-                                   int N, int K, const int* tiles, const int* n_tiles, int max_tiles, int gelu,
+                                   int N, int K, const int* tiles, const int* n_tiles, int max_tiles, int act,
                                    int rows_per_tile, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return 0;
+  const int gelu = act == 1, gated_a = act == 2;
   if (K % 32 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
     return (int)cudaErrorInvalidValue;
   dim3 grid((N + 127) / 128, max_tiles);
@@ -572,7 +613,7 @@ BSPEC_API int bspec_moe_skinny_mma(const void* A, const int* perm, int top, cons
   do {                                                                                                              \
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_skinny_mma_kernel<TO, G, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     BSPEC_LAUNCH((moe_skinny_mma_kernel<TO, G, RT>), grid, 256, smem, stream, (const __nv_bfloat16*)A, perm, top,   \
-                 (const __nv_bfloat16*)W, (TO*)C, N, K, tiles, n_tiles);                                            \
+                 (const __nv_bfloat16*)W, (TO*)C, N, K, tiles, n_tiles, gated_a);                                   \
   } while (0)
 #define LR(TO, G) do { if (rows_per_tile == 16) LS(TO, G, 16); else LS(TO, G, 8); } while (0)
   if (out_dtype == BSPEC_F32) { if (gelu) LR(float, true); else LR(float, false); }

@@ -1331,7 +1331,9 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
                 out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
     """sum_k wts[t, k] * Wdown[e] gelu(Wup[e] h[t]) with e = ids[t, k].  ``w_up`` [E, ff, d], ``w_down`` [E, d, ff].
     ``glu``: the experts are gated, Wdown[e] (silu(Wgate[e] h) * (Wup[e] h)), and ``w_up`` holds [gate; up] as
-    [E, 2 ff, d]; the first product then leaves its result as it is and ``silu_mul`` follows.
+    [E, 2 ff, d]; the first product then leaves its result as it is, and this package's grouped kernels form
+    silu(gate) * up while they stage the rows of the second product (the vendor's grouped product is followed by
+    ``silu_mul`` instead).
     The (token, choice) rows are sorted by expert on the device; no count is read on the host."""
     _require_cuda(h, ids, wts, w_up, w_down)
     lib = load_library()
@@ -1339,6 +1341,7 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
     E, ff_up, _ = w_up.shape
     ff = ff_up // 2 if glu else ff_up                 # the down projection's inner size
     act = 0 if glu else 1                             # the first product's epilogue: 1 = gelu
+    act_down = 2 if glu else 0                        # the second product's operand: 2 = silu(gate) * up of [gate | up] rows
     top = ids.shape[1]
     slots = n * top
     assert w_up.shape == (E, ff_up, d) and w_down.shape == (E, d, ff) and w_up.is_contiguous() and w_down.is_contiguous()
@@ -1389,26 +1392,23 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
         y = torch.empty((slots, d), dtype=torch.float32, device=dev)
         _check(lib.bspec_moe_skinny_mma(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, ff_up, d,
                                         tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, act, mma_rows, _stream()), "moe_skinny_mma_up")
-        u = gated(u)
         _check(lib.bspec_moe_skinny_mma(u.data_ptr(), None, top, w_down.data_ptr(), y.data_ptr(), F32, d, ff,
-                                        tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 0, mma_rows, _stream()), "moe_skinny_mma_down")
+                                        tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, act_down, mma_rows, _stream()), "moe_skinny_mma_down")
     elif skinny:
         u = torch.empty((slots, ff_up), dtype=h.dtype, device=dev)
         y = torch.empty((slots, d), dtype=torch.float32, device=dev)
         _check(lib.bspec_moe_skinny(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, ff_up, d,
                                     tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, act, _stream()), "moe_skinny_up")
-        u = gated(u)
         _check(lib.bspec_moe_skinny(u.data_ptr(), None, top, w_down.data_ptr(), y.data_ptr(), F32, d, ff,
-                                    tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 0, _stream()), "moe_skinny_down")
+                                    tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, act_down, _stream()), "moe_skinny_down")
     else:
         u = torch.empty((slots, ff_up), dtype=h.dtype, device=dev)
         y = torch.empty((slots, d), dtype=torch.float32, device=dev)
         _check(lib.bspec_moe_grouped(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, code, ff_up,
                                      d, tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, BM, act, _stream()),
                "moe_grouped_up")
-        u = gated(u)
         _check(lib.bspec_moe_grouped(u.data_ptr(), None, top, w_down.data_ptr(), y.data_ptr(), code, F32, d, ff,
-                                     tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, BM, 0, _stream()),
+                                     tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, BM, act_down, _stream()),
                "moe_grouped_down")
     out = torch.empty((n, d), dtype=out_dtype, device=dev)
     _check(lib.bspec_moe_combine(y.data_ptr(), _dtype_code(y.dtype), inv.data_ptr(), wts.data_ptr(), top,

@@ -186,7 +186,8 @@ def test_squared_relu_feed_forward(ops, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,d,ff,E,top", [(7, 48, 16, 5, 2), (1, 100, 20, 7, 7), (40, 64, 32, 1, 1), (300, 320, 96, 12, 3),
-                                          (3, 320, 64, 8, 2)])
+                                          (3, 320, 64, 8, 2), (70, 64, 128, 16, 3), (210, 320, 16, 4, 1), (600, 96, 40, 3, 2),
+                                          (9, 256, 96, 2, 2), (2000, 128, 64, 8, 4)])
 def test_routed_gated_experts_with_softmax_over_the_chosen(ops, dtype, n, d, ff, E, top):
     """The router's logits are spread so that no choice is close; the weights are the softmax over the chosen logits
     alone, which the bias (large for one expert) shows: that expert is always chosen."""
@@ -298,6 +299,8 @@ LATENT_WINDOW_SHAPES = [
     (8, 96, 16, 16, [97, 40], [97, 300], 96),
     (32, 160, 32, 16, [1, 1], [1300, 31], 1000),
     (4, 64, 16, 8, [33, 1], [33, 2049], None),           # a sink without a window
+    (16, 512, 64, 16, [1, 1, 40], [700, 65, 300], 128),  # the widest latent the tensor-core kernel takes
+    (128, 256, 64, 64, [1, 2], [700, 65], 500),
 ]
 
 
