@@ -69,7 +69,8 @@ template <typename TD, typename TO, int SC, bool VEC>
 __global__ void stream_norm_kernel(float* __restrict__ x, const TD* __restrict__ pending,
                                    const float* __restrict__ vec, const float* __restrict__ mixw,
                                    const float* __restrict__ read, const void* __restrict__ weight, int w_dtype,
-                                   TO* __restrict__ out, int S_rt, int d, float eps) {
+                                   TO* __restrict__ out, int S_rt, int d, float eps,
+                                   const float* __restrict__ expand) {
   bspec::pdl_prologue(71);
   constexpr int SMAX = SC > 0 ? SC : MAX_STREAMS;
   constexpr int W = VEC ? 4 : 1;
@@ -88,14 +89,20 @@ __global__ void stream_norm_kernel(float* __restrict__ x, const TD* __restrict__
   float ss = 0.f;
   for (int i = W * threadIdx.x; i < d; i += W * blockDim.x) {
     float cur[W][SMAX];
+    // ``expand``: the streams do not exist yet; every one starts as this row [n, d] (the embedding) and is written
+    float4 first = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (expand != nullptr) {
+      if (VEC) first = *reinterpret_cast<const float4*>(expand + t * d + i);
+      else first.x = expand[t * d + i];
+    }
 #pragma unroll
     for (int s = 0; s < SMAX; ++s) {
       if (s < S) {
         if (VEC) {
-          const float4 v = *reinterpret_cast<const float4*>(xt + (size_t)s * d + i);
+          const float4 v = expand != nullptr ? first : *reinterpret_cast<const float4*>(xt + (size_t)s * d + i);
           cur[0][s] = v.x; cur[W > 1 ? 1 : 0][s] = v.y; cur[W > 1 ? 2 : 0][s] = v.z; cur[W > 1 ? 3 : 0][s] = v.w;
         } else {
-          cur[0][s] = xt[(size_t)s * d + i];
+          cur[0][s] = expand != nullptr ? first.x : xt[(size_t)s * d + i];
         }
       }
     }
@@ -117,6 +124,8 @@ __global__ void stream_norm_kernel(float* __restrict__ x, const TD* __restrict__
         for (int s = 0; s < SMAX; ++s)
           if (s < S) cur[c][s] = fresh[s];
       }
+    }
+    if (pending != nullptr || expand != nullptr) {
 #pragma unroll
       for (int s = 0; s < SMAX; ++s) {
         if (s < S) {
@@ -149,10 +158,10 @@ __global__ void stream_norm_kernel(float* __restrict__ x, const TD* __restrict__
       for (int c = 0; c < 4; ++c) y[c] = u_row[i + c] * r * load_as_f32(weight, w_dtype, i + c);
       store4<TO>(out + t * d + i, y);
     }
-    return;
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+      out[t * d + i] = from_f32<TO>(u_row[i] * r * load_as_f32(weight, w_dtype, i));
   }
-  for (int i = threadIdx.x; i < d; i += blockDim.x)
-    out[t * d + i] = from_f32<TO>(u_row[i] * r * load_as_f32(weight, w_dtype, i));
 }
 
 template <typename TD>
@@ -191,10 +200,11 @@ BSPEC_API int bspec_stream_expand(const float* src, float* x, int n, int S, int 
   return BSPEC_LAUNCH_CHECK();
 }
 
-// pending null: nothing joins.  read null: the streams are only updated (weight and out unused).
+// pending null: nothing joins.  read null: the streams are only updated (weight and out unused).  expand (float32
+// [n, d]) given: x is not read; every stream starts as that row and is written (the first norm of a step).
 BSPEC_API int bspec_stream_norm(float* x, const void* pending, int pending_dtype, const float* vec, const float* mixw,
                                 const float* read, const void* weight, int w_dtype, void* out, int out_dtype, int n,
-                                int S, int d, float eps, cudaStream_t stream) {
+                                int S, int d, float eps, const float* expand, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (S <= 0 || S > MAX_STREAMS || (pending != nullptr && mixw == nullptr) || (read != nullptr && (!weight || !out)))
     return (int)cudaErrorInvalidValue;
@@ -211,7 +221,7 @@ BSPEC_API int bspec_stream_norm(float* x, const void* pending, int pending_dtype
       cudaFuncSetAttribute(stream_norm_kernel<TD, TO, SC, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                            (int)smem);                                                                              \
     BSPEC_LAUNCH((stream_norm_kernel<TD, TO, SC, V>), n, threads, smem, stream, x, (const TD*)pending, vec, mixw,   \
-                 read, weight, w_dtype, (TO*)out, S, d, eps);                                                       \
+                 read, weight, w_dtype, (TO*)out, S, d, eps, expand); \
   } while (0)
 #define LN2(TD, TO, SC) do { if (v4) LN3(TD, TO, SC, true); else LN3(TD, TO, SC, false); } while (0)
 #define LN(TD, TO)                                                                                                  \

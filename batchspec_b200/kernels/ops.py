@@ -83,7 +83,7 @@ _SIGNATURES = {
     "bspec_relu_squared": [c_void_p, c_int, c_longlong, c_void_p],
     "bspec_stream_expand": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "bspec_stream_norm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-                          c_int, c_int, c_float, c_void_p],
+                          c_int, c_int, c_float, c_void_p, c_void_p],
     "bspec_stream_gather": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                             c_void_p],
     "bspec_tanh_softcap": [c_void_p, c_longlong, c_float, c_void_p],
@@ -420,22 +420,26 @@ def stream_expand(src: torch.Tensor, streams: int) -> torch.Tensor:
 
 def stream_norm(x: torch.Tensor, pending: Optional[torch.Tensor], vec: Optional[torch.Tensor],
                 mixw: Optional[torch.Tensor], read: Optional[torch.Tensor], weight: Optional[torch.Tensor] = None,
-                eps: float = 0.0, out: Optional[torch.Tensor] = None) -> None:
+                eps: float = 0.0, out: Optional[torch.Tensor] = None, expand: Optional[torch.Tensor] = None) -> None:
     """x [n, S, d] float32, in place: if ``pending`` [n, d] is given it joins all streams at once,
     x_t <- sum_s mix[s, t] x_s + write[t] * vec * pending, ``mixw`` = [mix (S x S, from x to) | write (S)] float32 and
     ``vec`` a float32 factor per column or None.  If ``read`` (float32 [S]) is given, out = RMS norm of
-    u = sum_s read[s] x_s times ``weight``, float32 arithmetic and one rounding."""
-    _require_cuda(x, pending, vec, mixw, read, weight, out)
+    u = sum_s read[s] x_s times ``weight``, float32 arithmetic and one rounding.  ``expand`` (float32 [n, d]): x holds
+    nothing yet; every stream starts as that row and is written (a step's first norm, which so spares a kernel that
+    only copies the embedding S times)."""
+    require("streams")
+    _require_cuda(x, pending, vec, mixw, read, weight, out, expand)
     n, S, d = _stream_args(x, pending, vec, mixw)
+    assert expand is None or (expand.dtype == torch.float32 and expand.shape == (n, d) and expand.is_contiguous())
     if read is not None:
         assert read.dtype == torch.float32 and read.numel() == S and read.is_contiguous()
         assert weight.numel() == d and out.shape == (n, d) and out.is_contiguous()
-    elif pending is None:
+    elif pending is None and expand is None:
         return
     _check(load_library().bspec_stream_norm(
         x.data_ptr(), _ptr(pending), _dtype_code(pending.dtype) if pending is not None else F32, _ptr(vec), _ptr(mixw),
         _ptr(read), _ptr(weight), _dtype_code(weight.dtype) if weight is not None else F32, _ptr(out),
-        _dtype_code(out.dtype) if out is not None else F32, n, S, d, float(eps), _stream()), "stream_norm")
+        _dtype_code(out.dtype) if out is not None else F32, n, S, d, float(eps), _ptr(expand), _stream()), "stream_norm")
 
 
 def stream_gather(x: torch.Tensor, pending: Optional[torch.Tensor], vec: Optional[torch.Tensor],

@@ -149,7 +149,9 @@ class DecoderModel:
         if s.streams:
             if first is not None:
                 raise ValueError("a model of several residual streams cannot add its input again before a run")
-            resid = ops.stream_expand(resid, s.streams)           # [n, S, d]
+            # [n, S, d]; the first run's norm fills it from the embedding rows (``expand_from``)
+            expand = resid
+            resid = torch.empty((n, s.streams, s.hidden_size), dtype=torch.float32, device=self.runtime.device)
         pending, scale, vec, mix = None, 1.0, None, None
         for e, run in enumerate(s.order):
             if run.add_input:
@@ -163,6 +165,8 @@ class DecoderModel:
                 extra["pending_vec"] = vec
             if mix is not None:
                 extra["pending_mix"] = mix
+            if s.streams and e == 0:
+                extra["expand_from"] = expand
             resid, pending = block.forward(resid, pending, ctx, self.caches[e], **extra)
             scale, vec = getattr(block, "residual_mult", 1.0), getattr(block, "residual_vec", None)
             mix = getattr(block, "residual_mix", None)

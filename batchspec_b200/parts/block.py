@@ -9,6 +9,7 @@ from typing import Dict
 
 import torch
 
+from ..kernels.ops import require as ops_require
 from .base import (BLOCKS, BRANCH_SCALES, FEED_FORWARDS, MIXERS, NORMS, STREAM_MIXES, Block, ParamSpec, Part, Runtime,
                    register_part)
 
@@ -111,6 +112,8 @@ class HyperConnection(Part):
                 "mix": ParamSpec((s, s), role="vector", init="ones_normal")}
 
     def bind(self, params):
+        if torch.device(self.runtime.device).type == "cuda":
+            ops_require("streams")                # the kernels of csrc/streams.cu
         self.read = params["in"].to(torch.float32).contiguous()
         self.write = torch.cat([params["mix"].to(torch.float32).reshape(-1),
                                 params["out"].to(torch.float32).reshape(-1)]).contiguous()
@@ -121,7 +124,8 @@ class HyperPreNormBlock(Block):
     """Pre-norm layer over several residual streams (hyper-connections), branches multiplied column by column by
     learned vectors: for the mixer and then the feed-forward, u = sum_s in[s] x_s; y = scale * sublayer(norm(u));
     x_t <- sum_s mix[s, t] x_s + out[t] * y.  The join of a branch and the read of the next one ride in the norm's
-    kernel; the last branch is returned with its vector and coefficients for whoever comes next."""
+    kernel; the last branch is returned with its vector and coefficients for whoever comes next.  ``expand_from``
+    [n, d]: ``resid`` holds nothing yet (the first run of a step) and every stream starts as this row."""
     SLOTS = {"norm1": NORMS, "mixer": MIXERS, "scale1": BRANCH_SCALES, "hc1": STREAM_MIXES, "norm2": NORMS,
              "ffn": FEED_FORWARDS, "scale2": BRANCH_SCALES, "hc2": STREAM_MIXES}
 
@@ -133,9 +137,10 @@ class HyperPreNormBlock(Block):
     def residual_mix(self):
         return self.hc2.write
 
-    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0, pending_vec=None, pending_mix=None):
+    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0, pending_vec=None, pending_mix=None,
+                expand_from=None):
         assert pending_scale == 1.0 and (pending is None or pending_mix is not None)
-        a = self.norm1.forward_streams(resid, pending, pending_vec, pending_mix, self.hc1.read)
+        a = self.norm1.forward_streams(resid, pending, pending_vec, pending_mix, self.hc1.read, expand_from)
         y = self.mixer.forward(a, ctx, cache)
         f = self.norm2.forward_streams(resid, y, self.scale1.weight, self.hc1.write, self.hc2.read)
         return resid, self.ffn.forward(f, ctx)
@@ -154,7 +159,8 @@ class HyperPreNormMixerBlock(Block):
     def residual_mix(self):
         return self.hc1.write
 
-    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0, pending_vec=None, pending_mix=None):
+    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0, pending_vec=None, pending_mix=None,
+                expand_from=None):
         assert pending_scale == 1.0 and (pending is None or pending_mix is not None)
-        a = self.norm1.forward_streams(resid, pending, pending_vec, pending_mix, self.hc1.read)
+        a = self.norm1.forward_streams(resid, pending, pending_vec, pending_mix, self.hc1.read, expand_from)
         return resid, self.mixer.forward(a, ctx, cache)

@@ -43,16 +43,17 @@ class RMSNorm(Norm):
         return out
 
 
-    def forward_streams(self, streams, delta=None, delta_vec=None, delta_mix=None, read=None):
+    def forward_streams(self, streams, delta=None, delta_vec=None, delta_mix=None, read=None, expand=None):
         """For a residual kept as several streams [n, S, d]: ``delta`` (times ``delta_vec`` per column) first joins
         the streams with the coefficients ``delta_mix``; then the rows u = sum_s read[s] x_s are normalised.
-        Without ``read`` only the streams are updated."""
+        Without ``read`` only the streams are updated.  ``expand`` [n, d]: the streams hold nothing yet and all
+        start as this row."""
         n, _, d = streams.shape
         out = torch.empty((n, d), dtype=self.runtime.dtype, device=streams.device) if read is not None else None
         if self.scalar_weight:
             raise ValueError("the norm over several streams takes a weight per column")
         with bucket("norm"):
-            ops.stream_norm(streams, delta, delta_vec, delta_mix, read, self.weight, self.eps, out)
+            ops.stream_norm(streams, delta, delta_vec, delta_mix, read, self.weight, self.eps, out, expand)
         return out
 
 

@@ -166,6 +166,13 @@ def test_streams_join_read_norm_and_sum(ops, dtype, n, S, d):
     assert (got.double() - want2).abs().max() <= (2e-5 if dtype == torch.float32 else 2e-2) * (1 + want2.abs().max())
     ops.stream_gather(x, None, None, None, rows, picked)
     assert (picked.double() - before.double().sum(1)[rows.long()]).abs().max() <= 1e-5 * (1 + before.abs().max() * S)
+    # a step's first norm fills the streams from the embedding rows itself: the same as expanding first
+    filled = torch.full((n, S, d), float("nan"), device=DEV)
+    got_fill = torch.empty(n, d, device=DEV, dtype=dtype)
+    ops.stream_norm(filled, None, None, None, in_c, (1 + w).contiguous(), eps, got_fill, expand=src)
+    expanded = ops.stream_expand(src, S)
+    ops.stream_norm(expanded, None, None, None, in_c, (1 + w).contiguous(), eps, got)
+    assert torch.equal(filled, expanded) and torch.equal(got_fill, got)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
