@@ -7,7 +7,8 @@
 //   stream_expand   x[t, s, :] = src[t, :] for every s
 //   stream_norm     the pending sublayer result joins the streams (if one is given), then the next sublayer's
 //                   input is read and RMS-normalised: out = u / sqrt(mean(u^2) + eps) * w, one rounding
-//                   (the counterpart of add + RMSNorm for one stream; without ``read`` it only updates)
+//                   (the counterpart of add + RMSNorm for one stream; without ``read`` it only updates; with
+//                   ``expand`` it fills the streams from one row per token first, as a step's first norm does)
 //   stream_gather   out[i, :] = sum_t x'_t of row rows[i], x' the streams after the pending result has joined
 //                   (nothing is written back): the rows that go to the final norm and the head
 // All arithmetic is float32; sums over the streams run in the order of the stream index.
@@ -18,7 +19,6 @@ namespace {
 
 constexpr int MAX_STREAMS = 16;
 
-template <typename T>
 __global__ void stream_expand_kernel(const float* __restrict__ src, float* __restrict__ x, int S, int d) {
   bspec::pdl_prologue(70);
   const size_t t = blockIdx.x;
@@ -196,7 +196,7 @@ __global__ void stream_gather_kernel(const float* __restrict__ x, const TD* __re
 BSPEC_API int bspec_stream_expand(const float* src, float* x, int n, int S, int d, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (S <= 0 || S > MAX_STREAMS) return (int)cudaErrorInvalidValue;
-  BSPEC_LAUNCH((stream_expand_kernel<float>), n, d >= 1024 ? 256 : 128, 0, stream, src, x, S, d);
+  BSPEC_LAUNCH((stream_expand_kernel), n, d >= 1024 ? 256 : 128, 0, stream, src, x, S, d);
   return BSPEC_LAUNCH_CHECK();
 }
 

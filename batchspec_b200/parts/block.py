@@ -9,7 +9,7 @@ from typing import Dict
 
 import torch
 
-from ..kernels.ops import require as ops_require
+from ..kernels import ops
 from .base import (BLOCKS, BRANCH_SCALES, FEED_FORWARDS, MIXERS, NORMS, STREAM_MIXES, Block, ParamSpec, Part, Runtime,
                    register_part)
 
@@ -113,7 +113,7 @@ class HyperConnection(Part):
 
     def bind(self, params):
         if torch.device(self.runtime.device).type == "cuda":
-            ops_require("streams")                # the kernels of csrc/streams.cu
+            ops.require("streams")                # the kernels of csrc/streams.cu
         self.read = params["in"].to(torch.float32).contiguous()
         self.write = torch.cat([params["mix"].to(torch.float32).reshape(-1),
                                 params["out"].to(torch.float32).reshape(-1)]).contiguous()
